@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the BT4-shape forward pass: positions per second on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|int8] [--batch B]
+    python bench.py --impl reference ...      # the CPU fp32 forward on the host cores
+
+One "step" is one forward pass over one batch of synthetic positions (seeded planes,
+N(0, 0.02) random-init weights of the BT4 shape; the trained network and lc0's benchmark
+positions are not available offline).  Positions are independent, so N GPUs run N replicas
+on disjoint batches with no collective on the data path ("weak" scaling: the per-GPU batch
+is fixed); torch.distributed (NCCL) is used only for the barrier and the max-over-ranks of
+the device-side time.  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "positions/sec at BT4 shape"
+CPU_SAMPLE_BATCH = 8
+
+
+def _peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.lines: list[str] = []
+        self.proc: subprocess.Popen | None = None
+        self.thread: threading.Thread | None = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def _dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, local, dist
+    torch.cuda.set_device(0)
+    return 0, 1, 0, None
+
+
+def _barrier(dist) -> None:
+    if dist is not None:
+        t = torch.zeros(1, device="cuda")
+        dist.all_reduce(t)
+    torch.cuda.synchronize()
+
+
+def _max_over_ranks(value: float, dist) -> float:
+    if dist is None:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _timed_steps(step, warmup: int, steps: int, dist) -> float:
+    """Milliseconds for exactly `steps` calls of `step`, CUDA events on the current stream, max over ranks."""
+    for _ in range(warmup):
+        step()
+    _barrier(dist)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    _barrier(dist)
+    return _max_over_ranks(start.elapsed_time(stop), dist)
+
+
+def _cpu_forward_rate(cfg, batch: int, repeats: int, warmup: int) -> tuple[float, float]:
+    """positions/s of the fp32 CPU oracle forward (the restatement of the reference graph)."""
+    from lczero_triton_b200 import mapping_table
+    from lczero_triton_b200.synthetic import synthetic_planes
+    from lczero_triton_b200.weights import random_weights
+    from oracle import bt4_oracle
+
+    weights = {k: v.float() for k, v in random_weights(cfg, 0).items()}
+    masks, values = synthetic_planes(batch, 0)
+    table = torch.tensor(mapping_table.values(), dtype=torch.int32)
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + repeats):
+            t0 = time.perf_counter()
+            bt4_oracle.forward(weights, cfg, masks, values, table=table)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return batch / med, med * 1e3
+
+
+def run_reference(args) -> None:
+    """The reference arm: the CPU fp32 forward on the host cores (the reference itself has no
+    executable forward: it is a graph compiler whose runtime lives outside its tree)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from lczero_triton_b200.config import BT4
+
+    threads = torch.get_num_threads()
+    rate, ms = _cpu_forward_rate(BT4, CPU_SAMPLE_BATCH, max(1, args.steps), max(1, args.warmup))
+    sample = f"BT4 fp32 forward, batch {CPU_SAMPLE_BATCH} per step, median of {max(1, args.steps)} steps"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": "positions/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BT4-shape forward (E1024 L15 H32 F1536), CPU fp32 oracle", "batch_per_step": CPU_SAMPLE_BATCH},
+        "cpu_baseline": {"value": rate, "unit": "positions/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": "positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run(args) -> None:
+    rank, world, local, dist = _dist_setup(args.gpus)
+    from lczero_triton_b200 import _lib, build
+    from lczero_triton_b200.config import BT4, INPUT_PLANES, POLICY_SIZE
+    from lczero_triton_b200.net import Bt4Net
+    from lczero_triton_b200.synthetic import synthetic_planes
+    from lczero_triton_b200.weights import random_weights
+
+    build.build()
+    cfg = BT4
+    batch = args.batch
+    peaks, peak_kind = _peaks()
+    weights = random_weights(cfg, 0)
+    net = Bt4Net(weights, cfg, mode=args.mode)
+    masks_h, values_h = synthetic_planes(batch, seed=1000 + rank)
+    masks_h, values_h = masks_h.pin_memory(), values_h.pin_memory()
+    masks_d, values_d = masks_h.cuda(), values_h.cuda()
+
+    def step_resident() -> None:
+        net.forward(masks_d, values_d)
+
+    # ---- device-resident throughput
+    step_resident()
+    torch.cuda.synchronize()
+    launches_before = _lib.launch_count()
+    step_resident()
+    launches_per_step = _lib.launch_count() - launches_before
+    sampler = ClockSampler(local)
+    sampler.start()
+    total_ms = _timed_steps(step_resident, args.warmup, args.steps, dist)
+    clocks = sampler.stop()
+    ms_per_step = total_ms / args.steps
+    value = world * batch * args.steps / (total_ms * 1e-3)
+
+    # ---- end to end through the public API: pinned host inputs in, host results out, every step
+    out_h = [torch.empty((batch, POLICY_SIZE), dtype=torch.float32).pin_memory(),
+             torch.empty((batch, 3), dtype=torch.float32).pin_memory(),
+             torch.empty((batch, 1), dtype=torch.float32).pin_memory()]
+    masks_in, values_in = torch.empty_like(masks_d), torch.empty_like(values_d)
+
+    def step_e2e() -> None:
+        masks_in.copy_(masks_h, non_blocking=True)
+        values_in.copy_(values_h, non_blocking=True)
+        outs = net.forward(masks_in, values_in)
+        for dst, src in zip(out_h, outs):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_ms = _timed_steps(step_e2e, max(1, args.warmup // 2), args.steps, dist)
+    e2e_value = world * batch * args.steps / (e2e_ms * 1e-3)
+    h2d = masks_h.numel() * 8 + values_h.numel() * 4
+    d2h = sum(t.numel() * 4 for t in out_h)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if args.mode == "bf16" else "int8", "data": "synthetic",
+        "config": {"workload": f"BT4-shape forward (E1024 L15 H32 F1536 smolgen 32->256), batch {batch} per GPU",
+                   "batch_per_gpu": batch, "global_batch": batch * world, "mode": args.mode, "parallelism": f"replicas x{world}",
+                   "l2": "working set per step (several GB of activations) far exceeds the 126 MB L2"},
+        "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+        "e2e": {"value": e2e_value, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+    }
+    flops = cfg.flops_per_position()
+    line["forward_tflops_per_gpu"] = flops * batch / (ms_per_step * 1e-3) / 1e12
+    line["forward_frac_of_sustained_bf16_peak"] = line["forward_tflops_per_gpu"] / peaks["bf16_tflops_sustained"]
+
+    if rank == 0 and world == 1:
+        # ---- roofline of the dominant kernel: the QKV projection GEMM (tcgen05), timed alone
+        from lczero_triton_b200 import ops
+
+        t_rows = batch * 64
+        layer = net.layers[0]["qkv"]
+        a = torch.randn((t_rows, cfg.embedding), device="cuda").to(torch.bfloat16)
+        out = torch.empty((t_rows, layer.n), dtype=torch.bfloat16, device="cuda")
+        if args.mode == "int8":
+            a = torch.randint(-127, 128, (t_rows, cfg.embedding), device="cuda", dtype=torch.int8)
+
+        def gemm_once() -> None:
+            ops.gemm(out, a, layer.w, m=t_rows, n=layer.n, k=layer.k, bias=layer.bias, w_layout=layer.layout,
+                     col_scale=layer.col_scale)
+
+        gemm_ms = _timed_steps(gemm_once, 3, 10, None) / 10
+        gemm_flops = 2.0 * t_rows * layer.n * layer.k
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * (2.0 if args.mode == "int8" else 1.0)
+        line["roofline"] = {
+            "bound": "tensor", "kernel": "gemm_tcgen05_kernel (QKV projection, M=%d N=%d K=%d)" % (t_rows, layer.n, layer.k),
+            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "peak_source": f"{peak_kind} burst bf16" + (" x2 nominal for int8" if args.mode == "int8" else ""),
+            "ms_per_launch": gemm_ms, "traffic": None,
+        }
+        # ---- CPU baseline beside it (bounded sample of the same workload)
+        if not args.no_cpu_baseline:
+            rate, ms = _cpu_forward_rate(cfg, CPU_SAMPLE_BATCH, 3, 1)
+            line["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": torch.get_num_threads(),
+                                    "kind": "port", "sample": f"BT4 fp32 forward, batch {CPU_SAMPLE_BATCH}, median of 3 after 1 warm-up ({ms:.0f} ms each)"}
+        # ---- p50 latency at batch 64 (whole forward replayed from a CUDA graph)
+        if not args.no_latency:
+            try:
+                m64, v64 = synthetic_planes(64, 7)
+                m64, v64 = m64.cuda(), v64.cuda()
+                net.forward(m64, v64)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    net.forward(m64, v64)
+                samples = []
+                for _ in range(10):
+                    graph.replay()
+                torch.cuda.synchronize()
+                for _ in range(200):
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    graph.replay()
+                    e.record()
+                    e.synchronize()
+                    samples.append(s.elapsed_time(e))
+                line["latency_batch64"] = {"p50_ms": statistics.median(samples), "p99_ms": sorted(samples)[197],
+                                           "how": "CUDA graph replay of the whole forward, 200 samples"}
+            except Exception as exc:  # noqa: BLE001 - reported, never fatal for the throughput line
+                line["latency_batch64"] = {"error": repr(exc)[:200]}
+    status, detail = _lib.device_status()
+    line["device_status"] = status
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--mode", default="bf16", choices=["bf16", "int8"])
+    ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-latency", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,196 @@
+/* lc0b200 — C ABI of the sm_100a kernels for the Lc0 BT4 transformer forward pass.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless its name ends in _host.
+ *  - "bf16" buffers hold __nv_bfloat16; the reference stores the same tensors as fp16.
+ *  - Argument order follows the reference's kernel ABI: output pointers first, then
+ *    inputs, then weights, then the integers the reference bakes into each op's
+ *    specialization dataclass (same names), then the CUDA stream (a cudaStream_t
+ *    passed as void*; NULL is the legacy default stream).
+ *  - Every entry point returns an LC0B200_* status, never throws, never allocates,
+ *    never synchronises (lc0b200_device_status is the one exception: it synchronises
+ *    the device to read the flag word).  In-place use (out == in) is allowed wherever
+ *    the reference graph does it.
+ *  - Citations "K/x.py" are packages/lczero-triton/src/lczero_triton/bt4/kernels/x.py,
+ *    "N" is packages/lczero-triton/src/lczero_triton/bt4/network.py and "T/x.py" is
+ *    packages/lczero-triton/tests/x.py of the reference.
+ */
+#ifndef LC0B200_H_
+#define LC0B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LC0B200_API __attribute__((visibility("default")))
+#else
+#define LC0B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LC0B200_OK = 0,
+  LC0B200_ERR_NULL_POINTER = 1,
+  LC0B200_ERR_BAD_SHAPE = 2,
+  LC0B200_ERR_UNSUPPORTED = 3,
+  LC0B200_ERR_MISALIGNED = 4,
+  LC0B200_ERR_CUDA = 5,
+  LC0B200_ERR_DEVICE_TIMEOUT = 6
+};
+
+/* Activation codes (K/add_vectors.py:19-26 has none/mish/relu, K/layer_norm.py:18-25 has
+ * none/mish/swish; one numbering serves both here). */
+enum { LC0B200_ACT_NONE = 0, LC0B200_ACT_MISH = 1, LC0B200_ACT_RELU = 2, LC0B200_ACT_SWISH = 3 };
+
+/* Batched-matmul operation codes, K/batched_matmul.py:19-23. */
+enum { LC0B200_BMM_BODY_QK = 0, LC0B200_BMM_BODY_ATTENTION_V = 1, LC0B200_BMM_POLICY_QK = 2 };
+
+/* GEMM element types and output kinds for lc0b200_gemm. */
+enum { LC0B200_IN_BF16 = 0, LC0B200_IN_INT8 = 1 };
+enum { LC0B200_OUT_BF16 = 0, LC0B200_OUT_F32 = 1, LC0B200_OUT_S32 = 2 };
+/* Layout of the weight operand: [K,N] row-major as the reference stores it (ONNX
+ * layout, N:1619-1639) or [N,K] row-major (pre-transposed at upload time). */
+enum { LC0B200_W_KN = 0, LC0B200_W_NK = 1 };
+
+LC0B200_API const char* lc0b200_version(void);
+LC0B200_API const char* lc0b200_status_string(int status);
+/* Synchronises the current device and returns LC0B200_ERR_DEVICE_TIMEOUT if any kernel's
+ * bounded wait ran out since the last call (detail_host[0..3] receives the flag words,
+ * may be NULL); clears the flag. */
+LC0B200_API int lc0b200_device_status(unsigned int* detail_host);
+
+/* ---- layout and element-wise ops ------------------------------------------------------ */
+
+/* K/expand_planes.py:26-42: out[p*64+sq] = bit sq of masks[p] ? bf16(values[p]) : 0. */
+LC0B200_API int lc0b200_expand_planes(void* out_bf16, const uint64_t* masks, const float* values,
+                          long long plane_count, void* stream);
+/* K/nchw_to_nhwc.py:26-44: first output_channels planes of [B,C,H*W] -> [B,H*W,output_channels]. */
+LC0B200_API int lc0b200_nchw_to_nhwc(void* out_bf16, const void* in_bf16, int batch_size, int input_channels,
+                         int output_channels, int height, int width, void* stream);
+/* K/preprocess_attention_body.py:26-61: out[b,sq,:] = cat(planes[b,:,sq], encoding[b,sq,:]). */
+LC0B200_API int lc0b200_preprocess_attention_body(void* out_bf16, const void* planes_bf16, const void* encoding_bf16,
+                                      int batch_size, int input_channels, int encoding_channels,
+                                      void* stream);
+/* K/input_gating.py:26-51: out = in * mult[sq,c] + add[sq,c], gates broadcast over the batch. */
+LC0B200_API int lc0b200_input_gating(void* out_bf16, const void* in_bf16, const void* mult_bf16, const void* add_bf16,
+                         int batch_size, int square_count, int channel_count, void* stream);
+/* K/add_vectors.py:37-66: out[i] = act(in[i] + bias[i mod bias_element_count]). */
+LC0B200_API int lc0b200_add_vectors(void* out_bf16, const void* in_bf16, const void* bias_bf16, long long element_count,
+                        int bias_element_count, int activation, void* stream);
+/* K/add_bias_batched.py:35-66: out[bt,row,c] = act(in[bt,row,c] + bias[bt,c]). */
+LC0B200_API int lc0b200_add_bias_batched(void* out_bf16, const void* in_bf16, const void* bias_bf16, int batch_count,
+                             long long row_count, int channel_count, int activation, void* stream);
+/* K/copy_type_converted.py:26-34: widen the final outputs to f32. */
+LC0B200_API int lc0b200_copy_type_converted(float* out_f32, const void* in_bf16, long long element_count, void* stream);
+/* K/policy_map.py:28-49: out[b,o] = in[b, table[o]], 0 when table[o] is out of range. */
+LC0B200_API int lc0b200_policy_map(void* out_bf16, const void* in_bf16, const int32_t* table, int batch_size,
+                       int input_element_count, int output_element_count, void* stream);
+
+/* ---- dense contractions ------------------------------------------------------------------ */
+
+/* K/matmul.py:57-116: C[m,n] = A[m,k] @ W[k,n], all row-major bf16, fp32 accumulation. */
+LC0B200_API int lc0b200_matmul(void* out_bf16, const void* a_bf16, const void* w_kn_bf16, long long m, int n, int k,
+                   void* stream);
+/* K/fused_qkv.py:30-123: three projections sharing A, separate weights and outputs. */
+LC0B200_API int lc0b200_fused_qkv_projection(void* q_bf16, void* k_bf16, void* v_bf16, const void* a_bf16,
+                                 const void* wq_kn_bf16, const void* wk_kn_bf16, const void* wv_kn_bf16,
+                                 long long m, int query_width, int key_width, int value_width, int k,
+                                 void* stream);
+/* K/fused_qkv.py:132-183: three row-broadcast bias adds in one launch (in place allowed). */
+LC0B200_API int lc0b200_fused_qkv_bias(void* q_out, const void* q_in, const void* q_bias, void* k_out, const void* k_in,
+                           const void* k_bias, void* v_out, const void* v_in, const void* v_bias,
+                           long long row_count, int query_width, int key_width, int value_width,
+                           void* stream);
+/* K/batched_matmul.py:68-210.  operation BODY_QK: out[B*H,64,64] = scale * Q_h K_h^T with heads
+ * interleaved in the channel dimension; POLICY_QK: out record stride 4288, contiguous operands;
+ * BODY_ATTENTION_V: out[B,64,H*n] = P[b,h] @ V[b,:,h] (scale ignored, may be NULL).
+ * scale points at one bf16 element on the device. */
+LC0B200_API int lc0b200_batched_matmul(void* out_bf16, const void* a_bf16, const void* b_bf16, const void* scale_bf16,
+                           int operation, long long batch_count, int m, int n, int k, int heads_per_sample,
+                           void* stream);
+
+/* General tensor-core GEMM with a fused epilogue (no counterpart as ONE reference kernel: it
+ * stands for K/matmul.py followed by K/add_bias_batched.py / K/add_vectors.py):
+ *   acc = A[m,k] @ W           (bf16 -> f32 accumulate, or int8 -> s32 accumulate)
+ *   y   = acc                  (bf16 inputs)
+ *       = acc * row_scale[m] * col_scale[n]   (int8 inputs; both scales f32, may be NULL = 1)
+ *   out = act(y + bias[n])     (bias bf16, may be NULL), stored as bf16 / f32,
+ *   or the raw s32 accumulator when out_kind == LC0B200_OUT_S32 (no scale, bias or activation).
+ * lda / ldw / ldc are row pitches in elements. */
+typedef struct lc0b200_gemm_args {
+  void* out;
+  const void* a;
+  const void* w;
+  const void* bias_bf16;
+  const float* row_scale;
+  const float* col_scale;
+  long long m;
+  int n;
+  int k;
+  long long lda;
+  long long ldw;
+  long long ldc;
+  int in_type;   /* LC0B200_IN_*  */
+  int out_kind;  /* LC0B200_OUT_* */
+  int w_layout;  /* LC0B200_W_*   */
+  int activation;
+} lc0b200_gemm_args;
+LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* args_host, void* stream);
+/* Same contract on the plain CUDA-core kernel (any shape / alignment; used for the tiny head
+ * layers and as an independent cross-check of the tensor-core kernel). */
+LC0B200_API int lc0b200_gemm_simt(const lc0b200_gemm_args* args_host, void* stream);
+/* Upload-time helper: dst[n,k] = src[k,n] (element_size 1 or 2). */
+LC0B200_API int lc0b200_transpose(void* dst, const void* src, int rows, int cols, int element_size, void* stream);
+
+/* ---- normalisation, softmax, attention -------------------------------------------------- */
+
+/* K/layer_norm.py:37-161 (argument order out,in,bias,skip,gamma,beta,alpha as
+ * T/test_layer_norm.py:412-415): v = act(in + bias); if has_skip v = alpha*v + skip;
+ * out = (v - mean) / sqrt(var + epsilon) * gamma + beta, population variance, fp32 math.
+ * alpha points at one bf16 element.  skip / alpha may be NULL when has_skip == 0.
+ * If q_out_int8 and q_scale_f32 are non-NULL the normalised row is additionally quantised
+ * per row (see lc0b200_quantize_rows) — no reference counterpart. */
+LC0B200_API int lc0b200_layer_norm(void* out_bf16, const void* in_bf16, const void* bias_bf16, const void* skip_bf16,
+                       const void* gamma_bf16, const void* beta_bf16, const void* alpha_bf16,
+                       long long row_count, int width, int activation, int has_skip, float epsilon,
+                       void* q_out_int8, float* q_scale_f32, void* stream);
+/* K/softmax_64.py:45-71: out = softmax over 64 of clamp(qk + smolgen, +-131008), NaN kept. */
+LC0B200_API int lc0b200_softmax_64(void* out_bf16, const void* scaled_qk_bf16, const void* smolgen_bf16,
+                       long long row_count, void* stream);
+/* Fused edge-biased attention for the 64-token board: N:1004-1047 (K/batched_matmul.py body_qk,
+ * K/softmax_64.py, K/batched_matmul.py body_attention_v) in one kernel, scores never leave the SM.
+ * q/k/v rows are tokens with heads interleaved in the channel dimension; ld* are row pitches in
+ * elements; bias is [B, H, 64, 64] bf16 (may be NULL); depth (per-head width) must be 32. */
+LC0B200_API int lc0b200_attention(void* out_bf16, const void* q_bf16, const void* k_bf16, const void* v_bf16,
+                      const void* bias_bf16, float scale, long long batch_size, int heads, int depth,
+                      long long ldq, long long ldk, long long ldv, long long ldo, void* stream);
+/* Symmetric per-row int8 quantisation (no reference counterpart; the reference has no int8 path):
+ * s = max|x| / 127 (1 if the row is all zero), q = clamp(rint(x / s), -127, 127), round-half-even. */
+LC0B200_API int lc0b200_quantize_rows(void* out_int8, float* scale_f32, const void* in_bf16, long long row_count,
+                          int width, long long ld_in, void* stream);
+
+/* ---- heads -------------------------------------------------------------------------------- */
+
+/* K/promotion_logits.py:67-145 (argument order records,keys,weights as the reference ABI):
+ * records[b,4096+s*24+t*3+c] = records[b,(48+s)*64+56+t] + keys[b,56+t,:].(W[:,c] + W[:,3]). */
+LC0B200_API int lc0b200_promotion_logits(void* records_bf16, const void* keys_bf16, const void* w_bf16, int batch_size,
+                             int width, void* stream);
+/* Input embedding front end, N:458-533 in two kernels instead of four:
+ * pos_in[b, sq*12 + c] = plane c of position b at square sq (c < 12)           (k1+k2)
+ * emb_in[b*64+sq, :]   = cat(112 plane values at sq, position[b, sq, :E])      (k1+k3) */
+LC0B200_API int lc0b200_embed_position_input(void* pos_in_bf16, const uint64_t* masks, const float* values,
+                                 int batch_size, void* stream);
+LC0B200_API int lc0b200_embed_concat(void* emb_in_bf16, const uint64_t* masks, const float* values,
+                         const void* position_bf16, int batch_size, int encoding_channels, void* stream);
+/* Policy tail, N:1307-1356 in one kernel: promotion logits + gather + f32 store.
+ * out[b,o] = f32(record value at table[o]) where record slots >= 4096 are computed on the fly. */
+LC0B200_API int lc0b200_policy_tail(float* out_f32, const void* records_bf16, const void* keys_bf16, const void* w_bf16,
+                        const int32_t* table, int batch_size, int width, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LC0B200_H_ */

@@ -1,0 +1,422 @@
+// Tensor-core GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with the
+// accumulator in TMEM, fused epilogue.  Replaces the reference's Triton _matmul_kernel
+// (bt4/kernels/matmul.py:57-116) and, through the fused epilogue, the bias/activation kernels
+// that follow it in the graph (bt4/kernels/add_bias_batched.py, add_vectors.py).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
+//   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
+//   warp 1      MMA issuer     (one elected lane issues tcgen05.mma; owns the TMEM allocation)
+//   warps 2..5  epilogue       (tcgen05.ld -> bias / dequant / activation -> global stores)
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Operands are staged K-major with the 128-byte swizzle;
+// the weight operand may instead be staged MN-major straight from the reference's [K,N] layout.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "gemm.h"
+#include "ptx.cuh"
+
+namespace lc0b200 {
+
+namespace {
+
+constexpr int kBM = 128;          // tile rows = TMEM lanes
+constexpr int kRowBytes = 128;    // one swizzle row: 64 bf16 or 128 int8 along K
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  // Keep below the 227 KB per-CTA limit with room for barriers and 1 KB alignment slack.
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct KernelParams {
+  void* out;
+  const bf16* bias;
+  const float* row_scale;
+  const float* col_scale;
+  long long m;
+  long long ldc;
+  int n;
+  int k;
+  int out_kind;
+  int activation;
+  int vec_ok;  // out / bias / col_scale are 16-byte aligned and ldc keeps rows aligned
+  unsigned int* status;
+};
+
+template <bool INT8>
+__device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* __restrict__ cs, int col) {
+  if (INT8) {
+    float y = static_cast<float>(static_cast<int>(raw)) * rs;
+    return cs != nullptr ? y * __ldg(cs + col) : y;
+  }
+  return __uint_as_float(raw);
+}
+
+template <int BN, bool INT8, bool W_KN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const KernelParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
+  constexpr int kUmmaK = INT8 ? 32 : 16;          // K per tcgen05.mma (32 bytes)
+  constexpr int kMmaPerStage = kElemsPerRow / kUmmaK;  // 4
+  constexpr int kPanelN = INT8 ? 128 : 64;        // N elements per 128-byte row (MN-major weight staging)
+  constexpr int kPanels = (BN + kPanelN - 1) / kPanelN;
+  constexpr int kPanelBytes = kElemsPerRow * kRowBytes;  // K rows x 128 B
+  static_assert(!W_KN || (BN % kPanelN == 0), "MN-major weight staging needs whole 128-byte panels");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = smem_base;
+  const uint32_t smem_b = smem_base + kStages * Cfg::kABytes;
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  const uint32_t bar_full = bar_base;                   // [kStages]
+  const uint32_t bar_empty = bar_base + 8 * kStages;    // [kStages]
+  const uint32_t bar_acc_full = bar_base + 16 * kStages;       // [2]
+  const uint32_t bar_acc_empty = bar_base + 16 * kStages + 16; // [2]
+  const uint32_t tmem_slot = bar_base + 16 * kStages + 32;
+  __shared__ int abort_flag_storage;
+  volatile int* abort_flag = &abort_flag_storage;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const long long m_tiles = (p.m + kBM - 1) / kBM;
+  const int n_tiles = (p.n + BN - 1) / BN;
+  const long long num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.k + kElemsPerRow - 1) / kElemsPerRow;
+
+  if (threadIdx.x == 0) {
+    abort_flag_storage = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(bar_acc_full + 8 * a, 1);
+      ptx::mbar_init(bar_acc_empty + 8 * a, kEpilogueWarps);
+    }
+    ptx::mbar_init_fence();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = static_cast<int>(tile / n_tiles) * kBM;
+        const int n0 = static_cast<int>(tile % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          ptx::mbar_expect_tx(full, Cfg::kStageBytes);
+          const int k0 = kb * kElemsPerRow;
+          ptx::tma_load_2d(smem_a + stage * Cfg::kABytes, &map_a, k0, m0, full);
+          if (W_KN) {
+#pragma unroll
+            for (int pnl = 0; pnl < kPanels; ++pnl) {
+              ptx::tma_load_2d(smem_b + stage * Cfg::kBBytes + pnl * kPanelBytes, &map_w, n0 + pnl * kPanelN, k0,
+                               full);
+            }
+          } else {
+            ptx::tma_load_2d(smem_b + stage * Cfg::kBBytes, &map_w, k0, n0, full);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc =
+          ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kBM), static_cast<uint32_t>(BN));
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        ok = ptx::mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 0x200u + acc);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 0x300u + stage);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_a + stage * Cfg::kABytes;
+          const uint32_t b_addr = smem_b + stage * Cfg::kBBytes;
+#pragma unroll
+          for (int j = 0; j < kMmaPerStage; ++j) {
+            // A: K-major, 8-row groups 1024 B apart; K advance = 32 B inside the swizzle row.
+            const uint64_t da = ptx::smem_desc_sw128(a_addr + j * 32, 16, 1024);
+            // W: K-major as A, or MN-major: 128-byte rows run along N, one row per K index,
+            //    8-row groups 1024 B apart (SBO), N panels kPanelBytes apart (LBO).
+            const uint64_t db = W_KN ? ptx::smem_desc_sw128(b_addr + j * kUmmaK * kRowBytes, kPanelBytes, 1024)
+                                     : ptx::smem_desc_sw128(b_addr + j * 32, 16, 1024);
+            const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+            if (INT8) {
+              ptx::mma_i8(tmem_d, da, db, idesc, accumulate);
+            } else {
+              ptx::mma_bf16(tmem_d, da, db, idesc, accumulate);
+            }
+          }
+          ptx::tc_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::tc_commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t local = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const long long m0 = (tile / n_tiles) * kBM;
+      const int n0 = static_cast<int>(tile % n_tiles) * BN;
+      const uint32_t acc = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      ok = ptx::mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status, 0x400u + acc);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const long long row = m0 + row_in_tile;
+      const bool row_ok = row < p.m;
+      const float rs = (INT8 && p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.n) break;  // warp-uniform
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(taddr_row + c * 32, v);
+        ptx::tc_wait_ld();
+        if (!row_ok) continue;
+        const bool full_chunk = (col0 + 32 <= p.n) && p.vec_ok;
+        if (p.out_kind == LC0B200_OUT_BF16) {
+          bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
+          if (full_chunk) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {  // 8 columns per 16-byte store
+              float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (p.bias != nullptr) {
+                const uint4 braw = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+                float2 t;
+                t = unpack_bf16x2(braw.x); b[0] = t.x; b[1] = t.y;
+                t = unpack_bf16x2(braw.y); b[2] = t.x; b[3] = t.y;
+                t = unpack_bf16x2(braw.z); b[4] = t.x; b[5] = t.y;
+                t = unpack_bf16x2(braw.w); b[6] = t.x; b[7] = t.y;
+              }
+              float y[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                y[j] = activate_rt(acc_value<INT8>(v[g * 8 + j], rs, p.col_scale, col0 + g * 8 + j) + b[j],
+                                   p.activation);
+              }
+              uint4 packed;
+              packed.x = pack_bf16x2(y[0], y[1]);
+              packed.y = pack_bf16x2(y[2], y[3]);
+              packed.z = pack_bf16x2(y[4], y[5]);
+              packed.w = pack_bf16x2(y[6], y[7]);
+              *reinterpret_cast<uint4*>(dst + g * 8) = packed;
+            }
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.n) {
+                float y = acc_value<INT8>(v[j], rs, p.col_scale, col0 + j);
+                if (p.bias != nullptr) y += __bfloat162float(p.bias[col0 + j]);
+                dst[j] = __float2bfloat16_rn(activate_rt(y, p.activation));
+              }
+            }
+          }
+        } else if (p.out_kind == LC0B200_OUT_F32) {
+          float* dst = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
+          #pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.n) {
+              float y = acc_value<INT8>(v[j], rs, p.col_scale, col0 + j);
+              if (p.bias != nullptr) y += __bfloat162float(p.bias[col0 + j]);
+              dst[j] = activate_rt(y, p.activation);
+            }
+          }
+        } else {  // raw accumulator bits (s32 for int8 inputs)
+          uint32_t* dst = reinterpret_cast<uint32_t*>(p.out) + row * p.ldc + col0;
+          if (full_chunk) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              *reinterpret_cast<uint4*>(dst + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+            }
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.n) dst[j] = v[j];
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] with a row pitch, tiled into [box_rows, box_cols] boxes
+// whose inner extent is exactly 128 bytes (the swizzle span).
+bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows, long long cols,
+              long long pitch_elems, int box_rows, int box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool INT8, bool W_KN>
+int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kElemsPerRow = INT8 ? 128 : 64;
+  constexpr int kPanelN = INT8 ? 128 : 64;
+  const int eb = INT8 ? 1 : 2;
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, g.a, eb, g.m, g.k, g.lda, kBM, kElemsPerRow)) return LC0B200_ERR_CUDA;
+  if (W_KN) {
+    if (!make_map(&map_w, g.w, eb, g.k, g.n, g.ldw, kElemsPerRow, kPanelN)) return LC0B200_ERR_CUDA;
+  } else {
+    if (!make_map(&map_w, g.w, eb, g.n, g.k, g.ldw, BN, kElemsPerRow)) return LC0B200_ERR_CUDA;
+  }
+  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN>;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+      return LC0B200_ERR_CUDA;
+    }
+    configured = true;
+  }
+  KernelParams p;
+  p.out = g.out;
+  p.bias = reinterpret_cast<const bf16*>(g.bias_bf16);
+  p.row_scale = g.row_scale;
+  p.col_scale = g.col_scale;
+  p.m = g.m;
+  p.ldc = g.ldc;
+  p.n = g.n;
+  p.k = g.k;
+  p.out_kind = g.out_kind;
+  p.activation = g.activation;
+  p.status = device_status_words();
+  if (p.status == nullptr) return LC0B200_ERR_CUDA;
+  const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
+  p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16));
+  const long long tiles = ceil_div_ll(g.m, kBM) * ceil_div_ll(g.n, BN);
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, p);
+  return launch_status();
+}
+
+template <bool INT8, bool W_KN>
+int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
+  // MN-major weight staging needs BN to be a whole number of 128-byte panels
+  // (64 bf16 or 128 int8 columns); narrower outputs just run a partly empty tile.
+  constexpr int kMinBn = W_KN ? (INT8 ? 128 : 64) : 32;
+  if (g.n > 128) return launch<256, INT8, W_KN>(g, stream);
+  if constexpr (kMinBn <= 128) {
+    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN>(g, stream);
+  }
+  if constexpr (kMinBn <= 64) {
+    if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN>(g, stream);
+  }
+  if constexpr (kMinBn <= 32) {
+    return launch<32, INT8, W_KN>(g, stream);
+  }
+  return LC0B200_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supported(const lc0b200_gemm_args& g) {
+  const int eb = g.in_type == LC0B200_IN_INT8 ? 1 : 2;
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0) return false;
+  if (!aligned16(g.a) || !aligned16(g.w)) return false;
+  if ((g.lda * eb) % 16 != 0 || (g.ldw * eb) % 16 != 0) return false;
+  if (g.m > 0x7FFFFF00LL) return false;  // tile coordinates are 32-bit
+  return true;
+}
+
+int gemm_tcgen05(const lc0b200_gemm_args& g, cudaStream_t stream) {
+  const bool int8 = g.in_type == LC0B200_IN_INT8;
+  const bool w_kn = g.w_layout == LC0B200_W_KN;
+  if (int8) return w_kn ? dispatch_bn<true, true>(g, stream) : dispatch_bn<true, false>(g, stream);
+  return w_kn ? dispatch_bn<false, true>(g, stream) : dispatch_bn<false, false>(g, stream);
+}
+
+}  // namespace lc0b200

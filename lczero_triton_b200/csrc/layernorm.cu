@@ -1,0 +1,255 @@
+// LayerNorm with the reference's fused prologue (bt4/kernels/layer_norm.py:37-161):
+//   v = act(x + bias); if has_skip: v = alpha * v + skip
+//   y = (v - mean) / sqrt(var + eps) * gamma + beta     (population variance, centred, fp32)
+// HBM-bound: each row is read once and kept on chip.  Rows up to 2048 wide are held in the
+// registers of ONE warp (warp-shuffle reductions, no shared memory, no block barrier); wider
+// rows (smolgen's 8192-wide LN) use one CTA per row with the row cached in shared memory.
+// The narrow kernel can also emit the per-row int8 quantisation of its result for the
+// int8 GEMM that consumes it.
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lc0b200 {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxGroups = 8;  // 16-byte groups of 8 channels per lane: 32 lanes x 8 x 8 = 2048 channels
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  float2 t;
+  t = unpack_bf16x2(raw.x); f[0] = t.x; f[1] = t.y;
+  t = unpack_bf16x2(raw.y); f[2] = t.x; f[3] = t.y;
+  t = unpack_bf16x2(raw.z); f[4] = t.x; f[5] = t.y;
+  t = unpack_bf16x2(raw.w); f[6] = t.x; f[7] = t.y;
+}
+
+struct LnParams {
+  bf16* out;
+  const bf16* in;
+  const bf16* bias;
+  const bf16* skip;
+  const bf16* gamma;
+  const bf16* beta;
+  const bf16* alpha;
+  int8_t* q_out;
+  float* q_scale;
+  long long rows;
+  int width;
+  int activation;
+  int has_skip;
+  float epsilon;
+};
+
+// One warp per row; GROUPS = ceil(width / 256) register groups per lane.
+template <int GROUPS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(const LnParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * static_cast<long long>(kWarpsPerBlock) + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const int groups = p.width >> 3;
+  const uint4* in = reinterpret_cast<const uint4*>(p.in + row * p.width);
+  const uint4* skip = p.has_skip ? reinterpret_cast<const uint4*>(p.skip + row * p.width) : nullptr;
+  const uint4* bias = reinterpret_cast<const uint4*>(p.bias);
+  const float alpha = p.has_skip ? __bfloat162float(*p.alpha) : 1.0f;
+
+  float v[GROUPS][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = lane + 32 * g;
+    if (idx < groups) {
+      float x[8], b[8];
+      unpack8(in[idx], x);
+      unpack8(__ldg(bias + idx), b);
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (p.has_skip) unpack8(skip[idx], s);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = activate_rt(x[j] + b[j], p.activation);
+        if (p.has_skip) t = alpha * t + s[j];
+        v[g][j] = t;
+        sum += t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[g][j] = 0.0f;
+    }
+  }
+  const float inv_width = 1.0f / static_cast<float>(p.width);
+  const float mean = warp_sum(sum) * inv_width;
+  float sq = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    if (lane + 32 * g < groups) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = v[g][j] - mean;
+        v[g][j] = c;
+        sq += c * c;
+      }
+    }
+  }
+  const float var = warp_sum(sq) * inv_width;
+  const float rstd = 1.0f / sqrtf(var + p.epsilon);
+
+  const uint4* gamma = reinterpret_cast<const uint4*>(p.gamma);
+  const uint4* beta = reinterpret_cast<const uint4*>(p.beta);
+  uint4* out = reinterpret_cast<uint4*>(p.out + row * p.width);
+  float amax = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = lane + 32 * g;
+    if (idx < groups) {
+      float ga[8], be[8];
+      unpack8(__ldg(gamma + idx), ga);
+      unpack8(__ldg(beta + idx), be);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y0 = v[g][2 * j] * rstd * ga[2 * j] + be[2 * j];
+        const float y1 = v[g][2 * j + 1] * rstd * ga[2 * j + 1] + be[2 * j + 1];
+        w[j] = pack_bf16x2(y0, y1);
+        // Keep the bf16-rounded result: the quantiser below must see what is stored.
+        const float2 r = unpack_bf16x2(w[j]);
+        v[g][2 * j] = r.x;
+        v[g][2 * j + 1] = r.y;
+        amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
+      }
+      out[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (p.q_out != nullptr) {
+    amax = warp_max(amax);
+    const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    if (lane == 0) p.q_scale[row] = s;
+    uint2* qdst = reinterpret_cast<uint2*>(p.q_out + row * p.width);
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      const int idx = lane + 32 * g;
+      if (idx < groups) {
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int q = max(-127, min(127, __float2int_rn(__fdiv_rn(v[g][j], s))));
+          packed[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << ((j & 3) * 8);
+        }
+        qdst[idx] = make_uint2(packed[0], packed[1]);
+      }
+    }
+  }
+}
+
+// One CTA per row, row cached in shared memory as fp32 (any width, any alignment).
+__global__ void __launch_bounds__(256) layer_norm_block_kernel(const LnParams p) {
+  extern __shared__ float row_cache[];
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const bf16* in = p.in + row * p.width;
+  const bf16* skip = p.has_skip ? p.skip + row * p.width : nullptr;
+  const float alpha = p.has_skip ? __bfloat162float(*p.alpha) : 1.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  auto block_sum = [&](float x) -> float {
+    x = warp_sum(x);
+    __syncthreads();
+    if (lane == 0) red[warp] = x;
+    __syncthreads();
+    float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.0f;
+    if (warp == 0) {
+      t = warp_sum(t);
+      if (lane == 0) red[0] = t;
+    }
+    __syncthreads();
+    return red[0];
+  };
+
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
+    float t = activate_rt(__bfloat162float(in[c]) + __bfloat162float(p.bias[c]), p.activation);
+    if (p.has_skip) t = alpha * t + __bfloat162float(skip[c]);
+    row_cache[c] = t;
+    sum += t;
+  }
+  const float mean = block_sum(sum) / static_cast<float>(p.width);
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
+    const float d = row_cache[c] - mean;
+    sq += d * d;
+  }
+  const float var = block_sum(sq) / static_cast<float>(p.width);
+  const float rstd = 1.0f / sqrtf(var + p.epsilon);
+  bf16* out = p.out + row * p.width;
+  for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
+    const float y = (row_cache[c] - mean) * rstd * __bfloat162float(p.gamma[c]) + __bfloat162float(p.beta[c]);
+    out[c] = __float2bfloat16_rn(y);
+  }
+}
+
+template <int GROUPS>
+int launch_warp(const LnParams& p, cudaStream_t st) {
+  const long long blocks = ceil_div_ll(p.rows, kWarpsPerBlock);
+  layer_norm_warp_kernel<GROUPS><<<static_cast<unsigned>(blocks), kWarpsPerBlock * 32, 0, st>>>(p);
+  return launch_status();
+}
+
+}  // namespace
+
+int layer_norm(void* out, const void* in, const void* bias, const void* skip, const void* gamma, const void* beta,
+               const void* alpha, long long rows, int width, int activation, int has_skip, float epsilon,
+               void* q_out, float* q_scale, cudaStream_t st) {
+  LnParams p;
+  p.out = reinterpret_cast<bf16*>(out);
+  p.in = reinterpret_cast<const bf16*>(in);
+  p.bias = reinterpret_cast<const bf16*>(bias);
+  p.skip = reinterpret_cast<const bf16*>(skip);
+  p.gamma = reinterpret_cast<const bf16*>(gamma);
+  p.beta = reinterpret_cast<const bf16*>(beta);
+  p.alpha = reinterpret_cast<const bf16*>(alpha);
+  p.q_out = reinterpret_cast<int8_t*>(q_out);
+  p.q_scale = q_scale;
+  p.rows = rows;
+  p.width = width;
+  p.activation = activation;
+  p.has_skip = has_skip;
+  p.epsilon = epsilon;
+  const bool vec = (width % 8 == 0) && width <= 256 * kMaxGroups && aligned16(out) && aligned16(in) &&
+                   aligned16(bias) && aligned16(gamma) && aligned16(beta) && (!has_skip || aligned16(skip)) &&
+                   (q_out == nullptr || aligned16(q_out));
+  if (vec) {
+    const int g = (width + 255) / 256;
+    if (g <= 1) return launch_warp<1>(p, st);
+    if (g <= 2) return launch_warp<2>(p, st);
+    if (g <= 3) return launch_warp<3>(p, st);
+    if (g <= 4) return launch_warp<4>(p, st);
+    if (g <= 6) return launch_warp<6>(p, st);
+    return launch_warp<8>(p, st);
+  }
+  if (q_out != nullptr) return LC0B200_ERR_UNSUPPORTED;
+  const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  if (smem > 200 * 1024) return LC0B200_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(layer_norm_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess) {
+      return LC0B200_ERR_CUDA;
+    }
+  }
+  if (rows > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
+  layer_norm_block_kernel<<<static_cast<unsigned>(rows), 256, smem, st>>>(p);
+  return launch_status();
+}
+
+}  // namespace lc0b200

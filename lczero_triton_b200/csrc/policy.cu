@@ -1,0 +1,96 @@
+// Policy-head tail kernels.
+//   promotion_logits: bt4/kernels/promotion_logits.py:67-145
+//   policy_tail: promotion logits + gather (bt4/kernels/policy_map.py:28-49) + f32 widening
+//                (bt4/kernels/copy_type_converted.py:26-34) in one pass over the record.
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lc0b200 {
+
+namespace {
+
+constexpr int kRecord = 4288;
+constexpr int kPromoStart = 4096;
+
+// offsets[t][c] = keys[b, 56+t, :] . (W[:, c] + W[:, 3]) for t in 0..7, c in 0..2; one warp per t.
+__device__ __forceinline__ void promotion_offsets(float (&dst)[3], const bf16* key_row, const bf16* w, int width,
+                                                  int lane) {
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k = lane; k < width; k += 32) {
+    const float x = __bfloat162float(key_row[k]);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[c] = fmaf(x, __bfloat162float(w[k * 4 + c]), acc[c]);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xFFFFFFFFu, acc[c], o);
+  }
+  dst[0] = acc[0] + acc[3];
+  dst[1] = acc[1] + acc[3];
+  dst[2] = acc[2] + acc[3];
+}
+
+// One CTA (8 warps) per position.
+__global__ void __launch_bounds__(256) promotion_logits_kernel(bf16* records, const bf16* __restrict__ keys,
+                                                               const bf16* __restrict__ w, int width) {
+  __shared__ float offs[8][3];
+  const long long b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float o[3];
+  promotion_offsets(o, keys + (b * 64 + 56 + warp) * width, w, width, lane);
+  if (lane == 0) { offs[warp][0] = o[0]; offs[warp][1] = o[1]; offs[warp][2] = o[2]; }
+  __syncthreads();
+  bf16* rec = records + b * kRecord;
+  if (threadIdx.x < 192) {
+    const int s = threadIdx.x / 24, t = (threadIdx.x % 24) / 3, c = threadIdx.x % 3;
+    const float qk = __bfloat162float(rec[(48 + s) * 64 + 56 + t]);
+    rec[kPromoStart + threadIdx.x] = __float2bfloat16_rn(qk + offs[t][c]);
+  }
+}
+
+__global__ void __launch_bounds__(256) policy_tail_kernel(float* __restrict__ out, const bf16* __restrict__ records,
+                                                          const bf16* __restrict__ keys, const bf16* __restrict__ w,
+                                                          const int32_t* __restrict__ table, int width) {
+  __shared__ float offs[8][3];
+  const long long b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float o[3];
+  promotion_offsets(o, keys + (b * 64 + 56 + warp) * width, w, width, lane);
+  if (lane == 0) { offs[warp][0] = o[0]; offs[warp][1] = o[1]; offs[warp][2] = o[2]; }
+  __syncthreads();
+  const bf16* rec = records + b * kRecord;
+  for (int i = threadIdx.x; i < 1858; i += 256) {
+    const int src = table[i];
+    float v = 0.0f;
+    if (src >= 0 && src < kPromoStart) {
+      v = __bfloat162float(rec[src]);
+    } else if (src >= kPromoStart && src < kRecord) {
+      const int j = src - kPromoStart;
+      const int s = j / 24, t = (j % 24) / 3, c = j % 3;
+      // Same rounding point as the unfused path: the promotion logit is a 16-bit record entry.
+      v = __bfloat162float(__float2bfloat16_rn(__bfloat162float(rec[(48 + s) * 64 + 56 + t]) + offs[t][c]));
+    }
+    out[b * 1858 + i] = v;
+  }
+}
+
+}  // namespace
+
+int promotion_logits(void* records, const void* keys, const void* w, int batch, int width, cudaStream_t st) {
+  promotion_logits_kernel<<<batch, 256, 0, st>>>(reinterpret_cast<bf16*>(records), reinterpret_cast<const bf16*>(keys),
+                                                 reinterpret_cast<const bf16*>(w), width);
+  return launch_status();
+}
+
+int policy_tail(float* out, const void* records, const void* keys, const void* w, const int32_t* table, int batch,
+                int width, cudaStream_t st) {
+  policy_tail_kernel<<<batch, 256, 0, st>>>(out, reinterpret_cast<const bf16*>(records),
+                                            reinterpret_cast<const bf16*>(keys), reinterpret_cast<const bf16*>(w),
+                                            table, width);
+  return launch_status();
+}
+
+}  // namespace lc0b200

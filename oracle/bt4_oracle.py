@@ -192,14 +192,24 @@ def policy_map(records: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 def forward(weights: Mapping[str, torch.Tensor], cfg, masks: torch.Tensor, values: torch.Tensor, *,
             table: torch.Tensor, round_to: torch.dtype | None = None,
-            taps: dict[str, torch.Tensor] | None = None):
+            taps: dict[str, torch.Tensor] | None = None, int8: bool = False):
     """fp32 forward in the reference's op order (N:343-643 embedding, N:705-850
     smolgen, N:853-1076 attention, N:1079-1186 FFN, N:1189-1356 policy,
     N:1409-1550 value / moves-left).
 
     Returns ``(policy f32[B,1858], wdl f32[B,3] raw logits, mlh f32[B,1])``.
     ``taps`` (optional dict) receives named intermediates for per-stage diffing.
+    ``int8=True`` sends the four large GEMMs of every encoder layer (QKV, attention
+    output, FFN dense1 and dense2) through ``oracle/int8_oracle.py`` on bf16-rounded
+    activations; there is no reference counterpart for that mode.
     """
+    if int8:
+        from oracle import int8_oracle
+
+        def big(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+            return int8_oracle.linear(a.to(torch.bfloat16), weight)
+    else:
+        big = matmul
     w = {k: v.float() for k, v in weights.items()}
     r = lambda x: _round(x, round_to)  # noqa: E731
     b = masks.shape[0]
@@ -240,19 +250,19 @@ def forward(weights: Mapping[str, torch.Tensor], cfg, masks: torch.Tensor, value
                            w[f"{p}/smolgen/ln2/w/bias"], "swish", eps))
         smolgen = r(matmul(gen.reshape(b * h, -1), w["/const/smolgen_w"])).reshape(b, h, SQUARES, SQUARES)
 
-        q = r(matmul(body, w[f"{p}/mha/Q/w/w"]) + w[f"{p}/mha/Q/b/w"])
-        k = r(matmul(body, w[f"{p}/mha/K/w/w"]) + w[f"{p}/mha/K/b/w"])
-        v = r(matmul(body, w[f"{p}/mha/V/w/w"]) + w[f"{p}/mha/V/b/w"])
+        q = r(big(body, w[f"{p}/mha/Q/w/w"]) + w[f"{p}/mha/Q/b/w"])
+        k = r(big(body, w[f"{p}/mha/K/w/w"]) + w[f"{p}/mha/K/b/w"])
+        v = r(big(body, w[f"{p}/mha/V/w/w"]) + w[f"{p}/mha/V/b/w"])
         scale = float(w[f"{p}/mha/QK/scale/w"])
         qk = body_qk(q.reshape(b, SQUARES, d), k.reshape(b, SQUARES, d), scale, h)
         probs = softmax_64(qk, smolgen)
         merged = r(attention_v(probs, v.reshape(b, SQUARES, d)).reshape(t, d))
-        branch = r(matmul(merged, w[f"{p}/mha/out/dense/w/w"]))
+        branch = r(big(merged, w[f"{p}/mha/out/dense/w/w"]))
         attended = r(layer_norm(branch, w[f"{p}/mha/out/dense/b/w"], w[f"{p}/ln1/w/scale"], w[f"{p}/ln1/w/bias"],
                                 "none", eps, skip=body, alpha=w[f"{p}/alpha*input/w"]))
-        hidden = r(add_bias_batched(matmul(attended, w[f"{p}/ffn/dense1/w/w"])[None],
+        hidden = r(add_bias_batched(big(attended, w[f"{p}/ffn/dense1/w/w"])[None],
                                     w[f"{p}/ffn/dense1/b/w"][None], "mish")[0])
-        branch = r(matmul(hidden, w[f"{p}/ffn/dense2/w/w"]))
+        branch = r(big(hidden, w[f"{p}/ffn/dense2/w/w"]))
         body = r(layer_norm(branch, w[f"{p}/ffn/dense2/b/w"], w[f"{p}/ln2/w/scale"], w[f"{p}/ln2/w/bias"],
                             "none", eps, skip=attended, alpha=w[f"{p}/ffn/alpha/w"]))
         tap(f"encoder{i}", body)

@@ -1,0 +1,131 @@
+"""End-to-end parity of the GPU forward pass with the fp32 CPU oracle.
+
+Tolerance (stated by the build's target): policy logits and WDL within 1e-2 absolute or 1 %
+relative of the fp32 forward.  Random N(0, 0.02) weights give small logits, so the tests also
+bound the error relative to each output's spread, which is the discriminating check.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import bt4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    from lczero_triton_b200 import build
+
+    build.build()
+    import lczero_triton_b200 as package
+    from lczero_triton_b200 import config, mapping_table, net, synthetic, weights
+
+    return {"config": config, "net": net, "synthetic": synthetic, "weights": weights,
+            "table": torch.tensor(mapping_table.values(), dtype=torch.int32), "package": package}
+
+
+def _within_tolerance(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
+    err = (got - want).abs()
+    return (err <= 1e-2) | (err <= 1e-2 * want.abs())
+
+
+def _relative_to_spread(got: torch.Tensor, want: torch.Tensor) -> float:
+    return float((got - want).abs().max() / want.std().clamp_min(1e-12))
+
+
+def _run(pkg, cfg, batch: int, *, mode: str = "bf16", layout: str = "nk", seed: int = 0, std: float = 0.02):
+    weights = pkg["weights"].random_weights(cfg, seed, std=std)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, seed)
+    net = pkg["net"].Bt4Net(weights, cfg, mode=mode, weight_layout=layout)
+    taps: dict[str, torch.Tensor] = {}
+    policy, wdl, mlh = net.forward(masks.cuda(), values.cuda(), taps=taps)
+    torch.cuda.synchronize()
+    from lczero_triton_b200 import _lib
+
+    status, detail = _lib.device_status()
+    assert status == 0, f"a kernel's bounded wait ran out: {detail}"
+    return weights, masks, values, (policy.cpu(), wdl.cpu(), mlh.cpu()), {k: v.float().cpu() for k, v in taps.items()}
+
+
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+@pytest.mark.parametrize("batch", [1, 3, 32])
+def test_tiny_network_matches_fp32_oracle(pkg, batch, layout) -> None:
+    cfg = pkg["config"].TINY
+    weights, masks, values, got, taps = _run(pkg, cfg, batch, layout=layout)
+    want_taps: dict[str, torch.Tensor] = {}
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps)
+    for name in ("embedding", *[f"encoder{i}" for i in range(cfg.layers)]):
+        torch.testing.assert_close(taps[name], want_taps[name], rtol=0, atol=6e-2, msg=lambda m: f"{name}: {m}")
+    for g, w, label in zip(got, want, ("policy", "wdl", "mlh")):
+        assert _within_tolerance(g, w).all(), label
+    assert _relative_to_spread(got[0], want[0]) < 0.15
+    assert _relative_to_spread(got[1], want[1]) < 0.15
+
+
+@pytest.mark.parametrize("name", ["BT3", "BT4"])
+def test_full_shape_networks_match_fp32_oracle(pkg, name) -> None:
+    cfg = getattr(pkg["config"], name)
+    weights, masks, values, got, taps = _run(pkg, cfg, 4)
+    want_taps: dict[str, torch.Tensor] = {}
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps)
+    for stage in ("embedding", "encoder0", f"encoder{cfg.layers - 1}"):
+        err = (taps[stage] - want_taps[stage]).abs()
+        assert float(err.max()) < 0.12 and float(err.mean()) < 1.2e-2, (stage, float(err.max()), float(err.mean()))
+    for g, w, label in zip(got, want, ("policy", "wdl", "mlh")):
+        assert _within_tolerance(g, w).all(), label
+    assert _relative_to_spread(got[0], want[0]) < 0.15
+    assert _relative_to_spread(got[1], want[1]) < 0.15
+
+
+def test_larger_weights_keep_relative_accuracy(pkg) -> None:
+    """N(0, 0.02) weights make every logit small; a wider init exercises the same path with O(1) logits."""
+    cfg = pkg["config"].TINY
+    weights, masks, values, got, _ = _run(pkg, cfg, 8, seed=3, std=0.08)
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"])
+    assert float(want[0].abs().max()) > 0.2
+    assert _relative_to_spread(got[0], want[0]) < 0.2
+    torch.testing.assert_close(got[1], want[1], rtol=5e-2, atol=2e-2)
+    torch.testing.assert_close(got[2], want[2], rtol=5e-2, atol=2e-2)
+
+
+def test_positions_are_independent(pkg) -> None:
+    """Sharding by position is exact: a position's result does not depend on its batch neighbours."""
+    cfg = pkg["config"].TINY
+    weights = pkg["weights"].random_weights(cfg, 1)
+    masks, values = pkg["synthetic"].synthetic_planes(16, 1)
+    net = pkg["net"].Bt4Net(weights, cfg)
+    full = [x.clone() for x in net.forward(masks.cuda(), values.cuda())]
+    half = [x.clone() for x in net.forward(masks[8:].cuda(), values[8:].cuda())]
+    for f, h in zip(full, half):
+        assert torch.equal(f[8:], h)
+
+
+@pytest.mark.parametrize("name", ["TINY", "BT4"])
+def test_int8_network_tracks_int8_oracle(pkg, name) -> None:
+    cfg = getattr(pkg["config"], name)
+    batch = 4
+    weights, masks, values, got, taps = _run(pkg, cfg, batch, mode="int8")
+    want_taps: dict[str, torch.Tensor] = {}
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps, int8=True,
+                     round_to=torch.bfloat16)
+    err = (taps["encoder0"] - want_taps["encoder0"]).abs()
+    assert float(err.mean()) < 2e-2, float(err.mean())
+    for g, w, label in zip(got, want, ("policy", "wdl", "mlh")):
+        assert _within_tolerance(g, w).all(), label
+    fp32 = O.forward(weights, cfg, masks, values, table=pkg["table"])
+    assert _relative_to_spread(got[0], fp32[0]) < 0.5  # reported, not promised: int8 vs fp32
+
+
+def test_forward_rejects_bad_inputs(pkg) -> None:
+    cfg = pkg["config"].TINY
+    net = pkg["net"].Bt4Net(pkg["weights"].random_weights(cfg, 0), cfg)
+    masks, values = pkg["synthetic"].synthetic_planes(2, 0)
+    with pytest.raises(ValueError):
+        net.forward(masks.cuda().int(), values.cuda())
+    with pytest.raises(ValueError):
+        net.forward(masks.cuda()[:, :100], values.cuda()[:, :100])
+    with pytest.raises(ValueError):
+        net.forward(masks, values)

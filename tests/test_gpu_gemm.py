@@ -1,0 +1,172 @@
+"""GPU parity of the tensor-core GEMM (tcgen05 + TMA) through the C ABI.
+
+bf16: compared with an fp32 matmul of the same bf16 values; the kernel accumulates in fp32
+(TMEM) and rounds once to bf16, so the tolerance is one bf16 ulp of the result plus the fp32
+accumulation-order noise.  int8: the s32 accumulators must equal the CPU integer product bit
+for bit.  Every case is also run on the plain CUDA-core kernel as an independent cross-check.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import bt4_oracle as O
+from oracle import int8_oracle
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lczero_triton_b200 import build, ops as module
+
+    build.build()
+    return module
+
+
+@pytest.fixture(autouse=True)
+def _no_device_timeouts():
+    yield
+    from lczero_triton_b200 import _lib
+
+    status, detail = _lib.device_status()
+    assert status == 0, f"a kernel's bounded wait ran out: {detail}"
+
+
+def _gen(seed: int) -> torch.Generator:
+    return torch.Generator().manual_seed(seed)
+
+
+def _operands(m: int, n: int, k: int, seed: int):
+    a = (torch.randn((m, k), generator=_gen(seed)) * 0.5).to(BF16)
+    w = (torch.randn((k, n), generator=_gen(seed + 1)) * 0.5).to(BF16)
+    return a, w
+
+
+def _check(got: torch.Tensor, want: torch.Tensor, k: int) -> None:
+    # |result| ~ 0.25 sqrt(k); one bf16 ulp of that plus a little.
+    atol = 0.25 * (k ** 0.5) * 2 ** -8 * 2 + 1e-3
+    torch.testing.assert_close(got.float().cpu(), want, rtol=8e-3, atol=atol)
+
+
+SHAPES = [
+    (128, 256, 64), (128, 256, 1024), (256, 1024, 1024), (1024, 1536, 1024), (640, 1024, 1536),
+    (512, 3072, 1024), (300, 1000, 520), (64, 32768, 768), (4096, 32, 1024), (4096, 16, 128),
+    (77, 64, 2048), (130, 128, 8192), (2048, 4096, 256), (33, 8192, 256), (1000, 1024, 624), (5, 128, 128),
+]
+
+
+@pytest.mark.parametrize(("m", "n", "k"), SHAPES)
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_bf16_gemm_matches_fp32_matmul(ops, m, n, k, layout) -> None:
+    from lczero_triton_b200 import _lib
+
+    a, w = _operands(m, n, k, 100)
+    want = O.matmul(a, w)
+    out = torch.full((m, n), float("nan"), dtype=BF16, device="cuda")
+    if layout == "nk":
+        ops.gemm(out, a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, w_layout=_lib.W_NK)
+    else:
+        ops.gemm(out, a.cuda(), w.cuda(), m=m, n=n, k=k, w_layout=_lib.W_KN)
+    _check(out, want, k)
+
+
+@pytest.mark.parametrize("activation", ["none", "mish", "relu", "swish"])
+def test_bf16_gemm_bias_activation_epilogue(ops, activation) -> None:
+    from lczero_triton_b200 import _lib
+
+    m, n, k = 384, 1536, 1024
+    a, w = _operands(m, n, k, 110)
+    a, w = (a.float() * 0.2).to(BF16), (w.float() * 0.2).to(BF16)
+    bias = (torch.randn(n, generator=_gen(112)) * 0.5).to(BF16)
+    want = O.activate(O.matmul(a, w) + bias.float(), activation)
+    out = torch.empty((m, n), dtype=BF16, device="cuda")
+    ops.gemm(out, a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, bias=bias.cuda(), activation=activation,
+             w_layout=_lib.W_NK)
+    torch.testing.assert_close(out.float().cpu(), want, rtol=1e-2, atol=1e-2)
+
+
+def test_bf16_gemm_strided_output_and_f32_output(ops) -> None:
+    from lczero_triton_b200 import _lib
+
+    m, n, k = 200, 128, 256
+    a, w = _operands(m, n, k, 120)
+    want = O.matmul(a, w)
+    wide = torch.zeros((m, 3 * n), dtype=BF16, device="cuda")
+    ops.gemm(wide[:, n:2 * n], a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, ldc=3 * n, w_layout=_lib.W_NK)
+    _check(wide[:, n:2 * n], want, k)
+    assert wide[:, :n].abs().sum() == 0 and wide[:, 2 * n:].abs().sum() == 0
+    f32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.gemm(f32, a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, w_layout=_lib.W_NK)
+    torch.testing.assert_close(f32.cpu(), want, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize(("m", "n", "k"), [(7, 37, 11), (64, 3, 128), (200, 1, 128), (33, 4, 100)])
+def test_reference_layout_matmul_on_unaligned_shapes(ops, m, n, k) -> None:
+    """Shapes TMA cannot address (the reference tests 7 x 37 x 11, test_matmul.py:115-138) take the
+    CUDA-core kernel behind the same entry point."""
+    a, w = _operands(m, n, k, 130)
+    out = torch.empty((m, n), dtype=BF16, device="cuda")
+    ops.matmul(out, a.cuda(), w.cuda(), m, n, k)
+    _check(out, O.matmul(a, w), k)
+
+
+@pytest.mark.parametrize(("m", "n", "k"), [(128, 256, 128), (300, 1000, 528), (1024, 3072, 1024), (512, 1024, 1536),
+                                            (64, 128, 4096), (4096, 32, 1024)])
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_int8_gemm_accumulators_are_bit_exact(ops, m, n, k, layout) -> None:
+    from lczero_triton_b200 import _lib
+
+    aq = torch.randint(-127, 128, (m, k), generator=_gen(140), dtype=torch.int8)
+    wq = torch.randint(-127, 128, (k, n), generator=_gen(141), dtype=torch.int8)
+    want = int8_oracle.int_matmul(aq, wq)
+    out = torch.full((m, n), -1, dtype=torch.int32, device="cuda")
+    if layout == "nk":
+        ops.gemm(out, aq.cuda(), wq.t().contiguous().cuda(), m=m, n=n, k=k, w_layout=_lib.W_NK)
+    else:
+        if n % 16 != 0:
+            pytest.skip("TMA needs a 16-byte aligned row pitch for the [K,N] int8 layout")
+        ops.gemm(out, aq.cuda(), wq.cuda(), m=m, n=n, k=k, w_layout=_lib.W_KN)
+    assert torch.equal(out.cpu(), want)
+    simt = torch.empty_like(out)
+    ops.gemm(simt, aq.cuda(), wq.t().contiguous().cuda(), m=m, n=n, k=k, w_layout=_lib.W_NK, simt=True)
+    assert torch.equal(simt.cpu(), want)
+
+
+def test_int8_gemm_dequant_bias_mish_epilogue(ops) -> None:
+    from lczero_triton_b200 import _lib
+
+    m, n, k = 256, 1536, 1024
+    a = (torch.randn((m, k), generator=_gen(150))).to(BF16)
+    w = (torch.randn((k, n), generator=_gen(151)) * 0.02).to(BF16)
+    bias = (torch.randn(n, generator=_gen(152)) * 0.1).to(BF16)
+    aq, s_a = int8_oracle.quantize_rows(a)
+    wq, s_w = int8_oracle.quantize_weight(w)
+    want = O.activate(int8_oracle.dequant(int8_oracle.int_matmul(aq, wq), s_a, s_w, bias), "mish")
+    out = torch.empty((m, n), dtype=BF16, device="cuda")
+    ops.gemm(out, aq.cuda(), wq.t().contiguous().cuda(), m=m, n=n, k=k, bias=bias.cuda(), activation="mish",
+             row_scale=s_a.cuda(), col_scale=s_w.cuda(), w_layout=_lib.W_NK)
+    torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=4e-3)
+
+
+def test_gemm_linearity_at_full_size(ops) -> None:
+    """Size-independent property at the benchmark's row count: GEMM(a1 + a2) = GEMM(a1) + GEMM(a2)
+    when the sums are exact in bf16 (small integers), checked on sampled rows of a 262144-row problem."""
+    from lczero_triton_b200 import _lib
+
+    m, n, k = 262144, 1024, 1024
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    a1 = torch.randint(-3, 4, (m, k), generator=gen, device="cuda").to(BF16)
+    a2 = torch.randint(-3, 4, (m, k), generator=gen, device="cuda").to(BF16)
+    w = torch.randint(-2, 3, (n, k), generator=gen, device="cuda").to(BF16)
+    outs = []
+    for a in (a1, a2, a1 + a2):
+        out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        ops.gemm(out, a, w, m=m, n=n, k=k, w_layout=_lib.W_NK)
+        outs.append(out)
+    assert torch.equal(outs[0] + outs[1], outs[2])  # integer-valued, exact in fp32
+    rows = torch.tensor([0, 1, 127, 128, 131071, 200000, 262143], device="cuda")
+    want = a1[rows].float() @ w.float().t()
+    assert torch.equal(outs[0][rows], want)
