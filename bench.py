@@ -315,6 +315,85 @@ def run(args) -> None:
         dist.destroy_process_group()
 
 
+def run_kernel(args) -> None:
+    """Single-kernel measurements (one GPU): the GEMM at a given shape, the stand-alone
+    edge-biased attention operator (B x 64 tokens x 32 heads x 32), or the LayerNorm kernel.
+    Prints one JSON line with the CUDA-event time per launch and the achieved rate against the
+    measured peak that bounds the kernel."""
+    torch.cuda.set_device(0)
+    from lczero_triton_b200 import _lib, build, ops
+
+    build.build()
+    peaks, peak_kind = _peaks()
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    line: dict = {"kernel": args.kernel, "iters": args.iters}
+    if args.kernel == "gemm":
+        m, n, k = args.m, args.n, args.k
+        int8 = args.mode == "int8"
+        if int8:
+            a = torch.randint(-127, 128, (m, k), generator=gen, device="cuda", dtype=torch.int8)
+            w = torch.randint(-127, 128, (n, k) if args.layout == "nk" else (k, n), generator=gen, device="cuda",
+                              dtype=torch.int8)
+        else:
+            a = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+            w = (torch.randn((n, k) if args.layout == "nk" else (k, n), generator=gen, device="cuda") * 0.05).to(torch.bfloat16)
+        out_dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "s32": torch.int32}[args.out]
+        out = torch.empty((m, n), dtype=out_dtype, device="cuda")
+        bias = torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16) if args.epilogue != "none" else None
+        rs = torch.rand(m, generator=gen, device="cuda") if int8 and args.out != "s32" else None
+        cs = torch.rand(n, generator=gen, device="cuda") if int8 and args.out != "s32" else None
+        act = "mish" if args.epilogue == "bias_mish" else "none"
+        layout = _lib.W_NK if args.layout == "nk" else _lib.W_KN
+
+        def once() -> None:
+            ops.gemm(out, a, w, m=m, n=n, k=k, bias=bias, activation=act, w_layout=layout, row_scale=rs, col_scale=cs)
+
+        ms = _timed_steps(once, 3, args.iters, None) / args.iters
+        achieved = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * (2.0 if int8 else 1.0)
+        eb = 1 if int8 else 2
+        line.update({"shape": [m, n, k], "mode": args.mode, "layout": args.layout, "epilogue": args.epilogue,
+                     "out": args.out, "ms": ms, "achieved": achieved, "unit": "TFLOP/s", "peak": peak,
+                     "frac": achieved / peak, "peak_source": f"{peak_kind} burst bf16" + (" x2 nominal" if int8 else ""),
+                     "algorithmic_bytes": m * k * eb + n * k * eb + m * n * out.element_size()})
+    elif args.kernel == "attention":
+        b, h, d = args.batch, 32, 1024
+        q, k_, v = (torch.randn((b, 64, d), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(3))
+        bias = (torch.randn((b, h, 64, 64), generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        out = torch.empty((b, 64, d), dtype=torch.bfloat16, device="cuda")
+
+        def once() -> None:
+            ops.attention(out, q, k_, v, bias, 32 ** -0.5, b, h)
+
+        ms = _timed_steps(once, 3, args.iters, None) / args.iters
+        nbytes = 786432.0 * b
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        line.update({"batch": b, "heads": h, "depth": 32, "ms": ms, "achieved": achieved, "unit": "GB/s",
+                     "peak": peaks["hbm_gbs"], "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy",
+                     "algorithmic_bytes": nbytes, "tflops": 2.0 * 2 * b * h * 64 * 64 * 32 / (ms * 1e-3) / 1e12,
+                     "working_set_vs_l2": "larger" if nbytes > 126e6 else "fits in L2: not an HBM measurement"})
+    else:
+        rows, width = args.rows, args.width
+        x = torch.randn((rows, width), generator=gen, device="cuda").to(torch.bfloat16)
+        skip = torch.randn((rows, width), generator=gen, device="cuda").to(torch.bfloat16) if args.skip else None
+        vec = [torch.randn(width, generator=gen, device="cuda").to(torch.bfloat16) for _ in range(3)]
+        alpha = torch.tensor([0.5], device="cuda").to(torch.bfloat16) if args.skip else None
+        out = torch.empty_like(x)
+
+        def once() -> None:
+            ops.layer_norm(out, x, vec[0], vec[1], vec[2], row_count=rows, width=width, skip=skip, alpha=alpha)
+
+        ms = _timed_steps(once, 3, args.iters, None) / args.iters
+        nbytes = rows * width * 2.0 * (3 if args.skip else 2)
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        line.update({"rows": rows, "width": width, "skip": bool(args.skip), "ms": ms, "achieved": achieved, "unit": "GB/s",
+                     "peak": peaks["hbm_gbs"], "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy",
+                     "algorithmic_bytes": nbytes})
+    status, _ = _lib.device_status()
+    line["device_status"] = status
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -325,7 +404,22 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
+    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm"],
+                    help="measure one kernel instead of the whole forward pass")
+    ap.add_argument("--m", type=int, default=262144)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--layout", default="nk", choices=["nk", "kn"])
+    ap.add_argument("--epilogue", default="bias", choices=["none", "bias", "bias_mish"])
+    ap.add_argument("--out", default="bf16", choices=["bf16", "f32", "s32"])
+    ap.add_argument("--rows", type=int, default=262144)
+    ap.add_argument("--width", type=int, default=1024)
+    ap.add_argument("--skip", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
+    if args.kernel is not None:
+        run_kernel(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

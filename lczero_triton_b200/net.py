@@ -68,6 +68,8 @@ class Bt4Net:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise ValueError("Bt4Net needs a CUDA device; there is no CPU path")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self._layout = _lib.W_NK if weight_layout == "nk" else _lib.W_KN
         self._w = {k: v.to(device=self.device, dtype=torch.bfloat16).contiguous() for k, v in weights.items()}
         self._scalars = {k: float(v.float().reshape(-1)[0]) for k, v in weights.items() if v.numel() == 1}
