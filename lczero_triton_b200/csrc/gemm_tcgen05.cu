@@ -6,9 +6,13 @@
 // One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
 //   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one elected lane issues tcgen05.mma; owns the TMEM allocation)
-//   warps 2..5  epilogue       (tcgen05.ld -> bias / dequant / activation -> global stores)
+//   warps 2..    epilogue      (tcgen05.ld -> bias / dequant / activation -> bf16 -> swizzled
+//                              shared-memory staging -> TMA store; eight warps for BN >= 128:
+//                              two per TMEM lane quarter, each taking half of the columns)
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
-// overlaps the main loop of tile i+1.  Operands are staged K-major with the 128-byte swizzle;
+// overlaps the main loop of tile i+1.  bf16 results leave through cp.async.bulk.tensor stores
+// (full 128-byte lines, clipped at the matrix edge by the tensor map); f32 / raw s32 results and
+// unaligned outputs use direct stores.  Operands are staged K-major with the 128-byte swizzle;
 // the weight operand may instead be staged MN-major straight from the reference's [K,N] layout.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -23,8 +27,7 @@ namespace {
 
 constexpr int kBM = 128;          // tile rows = TMEM lanes
 constexpr int kRowBytes = 128;    // one swizzle row: 64 bf16 or 128 int8 along K
-constexpr int kThreads = 192;
-constexpr int kEpilogueWarps = 4;
+constexpr int kStagingBytesPerWarp = 32 * kRowBytes;  // 32 rows x 64 bf16 columns
 
 template <int BN>
 struct TileCfg {
@@ -34,7 +37,11 @@ struct TileCfg {
   // Keep below the 227 KB per-CTA limit with room for barriers and 1 KB alignment slack.
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpilogueWarps = (BN >= 128) ? 8 : 4;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+  static constexpr bool kTmaStore = BN >= 128;  // each epilogue warp then owns at least one 64-column group
+  static constexpr int kStagingBytes = kTmaStore ? kEpilogueWarps * kStagingBytesPerWarp : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct KernelParams {
@@ -48,7 +55,8 @@ struct KernelParams {
   int k;
   int out_kind;
   int activation;
-  int vec_ok;  // out / bias / col_scale are 16-byte aligned and ldc keeps rows aligned
+  int vec_ok;     // out / bias / col_scale are 16-byte aligned and ldc keeps rows aligned
+  int tma_store;  // bf16 output that a tensor map can address (map_out is valid)
   unsigned int* status;
 };
 
@@ -61,10 +69,69 @@ __device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* 
   return __uint_as_float(raw);
 }
 
+// One 32-column chunk of one accumulator row: dequantise, add bias, activate, pack to bf16.
+template <bool INT8>
+__device__ __forceinline__ void finish_chunk_bf16(const uint32_t (&v)[32], uint32_t (&packed)[16], int col0, float rs,
+                                                  const KernelParams& p) {
+  const bool vec = p.vec_ok && (col0 + 32 <= p.n);
+  float b[32], cs[32];
+  if (vec) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 braw = make_uint4(0u, 0u, 0u, 0u);
+      if (p.bias != nullptr) braw = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+      float2 t;
+      t = unpack_bf16x2(braw.x); b[g * 8 + 0] = t.x; b[g * 8 + 1] = t.y;
+      t = unpack_bf16x2(braw.y); b[g * 8 + 2] = t.x; b[g * 8 + 3] = t.y;
+      t = unpack_bf16x2(braw.z); b[g * 8 + 4] = t.x; b[g * 8 + 5] = t.y;
+      t = unpack_bf16x2(braw.w); b[g * 8 + 6] = t.x; b[g * 8 + 7] = t.y;
+    }
+    if (INT8) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float4 c = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (p.col_scale != nullptr) c = __ldg(reinterpret_cast<const float4*>(p.col_scale + col0 + g * 4));
+        cs[g * 4 + 0] = c.x; cs[g * 4 + 1] = c.y; cs[g * 4 + 2] = c.z; cs[g * 4 + 3] = c.w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const bool in = col0 + j < p.n;
+      b[j] = (in && p.bias != nullptr) ? __bfloat162float(p.bias[col0 + j]) : 0.0f;
+      if (INT8) cs[j] = (in && p.col_scale != nullptr) ? p.col_scale[col0 + j] : 1.0f;
+    }
+  }
+  float y[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x;
+    if (INT8) {
+      x = (static_cast<float>(static_cast<int>(v[j])) * rs) * cs[j];
+    } else {
+      x = __uint_as_float(v[j]);
+    }
+    y[j] = x + b[j];
+  }
+  // The activation code is uniform for the launch: branch once per chunk, not per element.
+  if (p.activation == LC0B200_ACT_MISH) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = act_mish(y[j]);
+  } else if (p.activation == LC0B200_ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.0f);
+  } else if (p.activation == LC0B200_ACT_SWISH) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = act_swish(y[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
+}
+
 template <int BN, bool INT8, bool W_KN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(TileCfg<BN>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const KernelParams p) {
+                    const __grid_constant__ CUtensorMap map_out, const KernelParams p) {
   using Cfg = TileCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
@@ -79,7 +146,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a = smem_base;
   const uint32_t smem_b = smem_base + kStages * Cfg::kABytes;
-  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  const uint32_t staging_base = smem_base + kStages * Cfg::kStageBytes;  // 1024-byte aligned
+  const uint32_t bar_base = staging_base + Cfg::kStagingBytes;
   const uint32_t bar_full = bar_base;                   // [kStages]
   const uint32_t bar_empty = bar_base + 8 * kStages;    // [kStages]
   const uint32_t bar_acc_full = bar_base + 16 * kStages;       // [2]
@@ -104,11 +172,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(bar_acc_full + 8 * a, 1);
-      ptx::mbar_init(bar_acc_empty + 8 * a, kEpilogueWarps);
+      ptx::mbar_init(bar_acc_empty + 8 * a, Cfg::kEpilogueWarps);
     }
     ptx::mbar_init_fence();
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_w);
+    if (p.tma_store) ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -203,13 +272,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;            // TMEM lane quarter this warp may access
+    const int ew = warp - 2;
+    const int quarter = warp & 3;              // TMEM lane quarter this warp may access
+    const int half = ew >> 2;                  // which share of the tile's columns (eight-warp layout)
+    constexpr int kColsPerWarp = BN / (Cfg::kEpilogueWarps / 4);
     const int row_in_tile = quarter * 32 + lane;
+    const uint32_t staging = staging_base + ew * kStagingBytesPerWarp;
+    const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;
     uint32_t local = 0;
     bool ok = true;
     for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const long long m0 = (tile / n_tiles) * kBM;
-      const int n0 = static_cast<int>(tile % n_tiles) * BN;
+      const int n0 = static_cast<int>(tile % n_tiles) * BN + half * kColsPerWarp;
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = ptx::mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status, 0x400u + acc);
@@ -218,82 +292,102 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.m;
       const float rs = (INT8 && p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
-      const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t taddr_row =
+          tmem_base + acc * BN + half * kColsPerWarp + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (tma_path) {
+        if constexpr (Cfg::kTmaStore) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.n) break;  // warp-uniform
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr_row + c * 32, v);
-        ptx::tc_wait_ld();
-        if (!row_ok) continue;
-        const bool full_chunk = (col0 + 32 <= p.n) && p.vec_ok;
-        if (p.out_kind == LC0B200_OUT_BF16) {
-          bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
-          if (full_chunk) {
+          for (int g = 0; g < kColsPerWarp / 64; ++g) {
+            const int col0 = n0 + g * 64;
+            if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
+            uint32_t v0[32], v1[32];
+            ptx::tmem_ld_32x32(taddr_row + g * 64, v0);
+            ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, v1);
+            ptx::tc_wait_ld();
+            uint32_t packed[32];
+            finish_chunk_bf16<INT8>(v0, *reinterpret_cast<uint32_t(*)[16]>(&packed[0]), col0, rs, p);
+            finish_chunk_bf16<INT8>(v1, *reinterpret_cast<uint32_t(*)[16]>(&packed[16]), col0 + 32, rs, p);
+            // The staging buffer is free once the previous store has finished reading it.
+            if (lane == 0) ptx::bulk_wait_read<0>();
+            __syncwarp();
+            // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor map expects:
+            // 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {  // 8 columns per 16-byte store
-              float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-              if (p.bias != nullptr) {
-                const uint4 braw = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
-                float2 t;
-                t = unpack_bf16x2(braw.x); b[0] = t.x; b[1] = t.y;
-                t = unpack_bf16x2(braw.y); b[2] = t.x; b[3] = t.y;
-                t = unpack_bf16x2(braw.z); b[4] = t.x; b[5] = t.y;
-                t = unpack_bf16x2(braw.w); b[6] = t.x; b[7] = t.y;
-              }
-              float y[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                y[j] = activate_rt(acc_value<INT8>(v[g * 8 + j], rs, p.col_scale, col0 + g * 8 + j) + b[j],
-                                   p.activation);
-              }
-              uint4 packed;
-              packed.x = pack_bf16x2(y[0], y[1]);
-              packed.y = pack_bf16x2(y[2], y[3]);
-              packed.z = pack_bf16x2(y[4], y[5]);
-              packed.w = pack_bf16x2(y[6], y[7]);
-              *reinterpret_cast<uint4*>(dst + g * 8) = packed;
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t addr = staging + lane * kRowBytes + ((c ^ (lane & 7)) << 4);
+              ptx::st_shared_v4(addr, packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
-          } else {
-            #pragma unroll
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&map_out, staging, col0, static_cast<int>(m0) + quarter * 32);
+              ptx::bulk_commit();
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kColsPerWarp / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.n) break;  // warp-uniform
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, v);
+          ptx::tc_wait_ld();
+          if (!row_ok) continue;
+          const bool full_chunk = (col0 + 32 <= p.n) && p.vec_ok;
+          if (p.out_kind == LC0B200_OUT_BF16) {
+            uint32_t packed[16];
+            finish_chunk_bf16<INT8>(v, packed, col0, rs, p);
+            bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
+            if (full_chunk) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                *reinterpret_cast<uint4*>(dst + g * 8) =
+                    make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) {
+                  const uint32_t w = packed[j >> 1];
+                  reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (w >> 16) : (w & 0xFFFFu));
+                }
+              }
+            }
+          } else if (p.out_kind == LC0B200_OUT_F32) {
+            float* dst = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
+#pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < p.n) {
                 float y = acc_value<INT8>(v[j], rs, p.col_scale, col0 + j);
                 if (p.bias != nullptr) y += __bfloat162float(p.bias[col0 + j]);
-                dst[j] = __float2bfloat16_rn(activate_rt(y, p.activation));
+                dst[j] = activate_rt(y, p.activation);
               }
             }
-          }
-        } else if (p.out_kind == LC0B200_OUT_F32) {
-          float* dst = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
-          #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + j < p.n) {
-              float y = acc_value<INT8>(v[j], rs, p.col_scale, col0 + j);
-              if (p.bias != nullptr) y += __bfloat162float(p.bias[col0 + j]);
-              dst[j] = activate_rt(y, p.activation);
-            }
-          }
-        } else {  // raw accumulator bits (s32 for int8 inputs)
-          uint32_t* dst = reinterpret_cast<uint32_t*>(p.out) + row * p.ldc + col0;
-          if (full_chunk) {
+          } else {  // raw accumulator bits (s32 for int8 inputs)
+            uint32_t* dst = reinterpret_cast<uint32_t*>(p.out) + row * p.ldc + col0;
+            if (full_chunk) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              *reinterpret_cast<uint4*>(dst + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-            }
-          } else {
-            #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.n) dst[j] = v[j];
+              for (int g = 0; g < 8; ++g) {
+                *reinterpret_cast<uint4*>(dst + g * 4) =
+                    make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) dst[j] = v[j];
+              }
             }
           }
         }
       }
+      // TMEM has been read out: hand the accumulator back before the stores drain.
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * acc);
     }
+    if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
+    __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
@@ -354,6 +448,11 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   } else {
     if (!make_map(&map_w, g.w, eb, g.n, g.k, g.ldw, BN, kElemsPerRow)) return LC0B200_ERR_CUDA;
   }
+  const int out_eb_probe = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
+  const bool tma_store = Cfg::kTmaStore && g.out_kind == LC0B200_OUT_BF16 && aligned16(g.out) &&
+                         ((g.ldc * out_eb_probe) % 16 == 0);
+  CUtensorMap map_out = map_a;  // placeholder when the direct-store epilogue is used
+  if (tma_store && !make_map(&map_out, g.out, 2, g.m, g.n, g.ldc, 32, 64)) return LC0B200_ERR_CUDA;
   auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN>;
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -376,10 +475,12 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   p.status = device_status_words();
   if (p.status == nullptr) return LC0B200_ERR_CUDA;
   const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
-  p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16));
+  p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16)) &&
+             (g.col_scale == nullptr || aligned16(g.col_scale));
+  p.tma_store = tma_store ? 1 : 0;
   const long long tiles = ceil_div_ll(g.m, kBM) * ceil_div_ll(g.n, BN);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, p);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, map_out, p);
   return launch_status();
 }
 

