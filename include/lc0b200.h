@@ -170,6 +170,14 @@ LC0B200_API int lc0b200_attention(void* out_bf16, const void* q_bf16, const void
  * s = max|x| / 127 (1 if the row is all zero), q = clamp(rint(x / s), -127, 127), round-half-even. */
 LC0B200_API int lc0b200_quantize_rows(void* out_int8, float* scale_f32, const void* in_bf16, long long row_count,
                           int width, long long ld_in, void* stream);
+/* One int8 dense layer on bf16 activations (no reference counterpart): quantise the rows of a
+ * (lc0b200_quantize_rows) into caller-provided scratch, then out = act(dequant(Aq @ Wq) + bias)
+ * (lc0b200_gemm with int8 inputs).  w_nk_int8 is [n,k] row-major, col_scale the per-output-channel
+ * weight scales.  scratch_q holds m*k bytes, scratch_scale m floats; both must be 16-byte aligned
+ * and may be reused as soon as the call's kernels have run. */
+LC0B200_API int lc0b200_linear_int8(void* out_bf16, const void* a_bf16, const void* w_nk_int8, const float* col_scale,
+                        const void* bias_bf16, void* scratch_q, float* scratch_scale, long long m, int n, int k,
+                        int activation, void* stream);
 
 /* ---- heads -------------------------------------------------------------------------------- */
 

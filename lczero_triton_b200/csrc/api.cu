@@ -22,6 +22,25 @@ unsigned int* device_status_words() {
 
 }  // namespace lc0b200
 
+namespace lc0b200 {
+
+int linear_int8(void* out, const void* a, const void* w_nk, const float* col_scale, const void* bias,
+                void* scratch_q, float* scratch_scale, long long m, int n, int k, int activation,
+                cudaStream_t stream) {
+  int st = quantize_rows(scratch_q, scratch_scale, a, m, k, k, stream);
+  if (st != LC0B200_OK) return st;
+  lc0b200_gemm_args g = {};
+  g.out = out; g.a = scratch_q; g.w = w_nk; g.bias_bf16 = bias;
+  g.row_scale = scratch_scale; g.col_scale = col_scale;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = k; g.ldw = k; g.ldc = n;
+  g.in_type = LC0B200_IN_INT8; g.out_kind = LC0B200_OUT_BF16; g.w_layout = LC0B200_W_NK;
+  g.activation = activation;
+  return gemm_tcgen05_supported(g) ? gemm_tcgen05(g, stream) : gemm_simt(g, stream);
+}
+
+}  // namespace lc0b200
+
 using namespace lc0b200;
 
 #define REQUIRE_PTR(p) \
@@ -268,6 +287,18 @@ LC0B200_API int lc0b200_quantize_rows(void* out, float* scale, const void* in, l
   REQUIRE_SHAPE(row_count >= 0 && width > 0 && ld_in >= width && row_count <= 8LL * 0x7FFFFFFF);
   if (row_count == 0) return LC0B200_OK;
   return quantize_rows(out, scale, in, row_count, width, ld_in, S(stream));
+}
+
+LC0B200_API int lc0b200_linear_int8(void* out, const void* a, const void* w_nk, const float* col_scale,
+                                    const void* bias, void* scratch_q, float* scratch_scale, long long m, int n,
+                                    int k, int activation, void* stream) {
+  REQUIRE_PTR(out); REQUIRE_PTR(a); REQUIRE_PTR(w_nk); REQUIRE_PTR(col_scale);
+  REQUIRE_PTR(scratch_q); REQUIRE_PTR(scratch_scale);
+  REQUIRE_SHAPE(m >= 0 && n > 0 && k > 0 && m <= 8LL * 0x7FFFFFFF);
+  REQUIRE_ALIGNED(scratch_q, 16); REQUIRE_ALIGNED(scratch_scale, 16);
+  if (!valid_activation(activation)) return LC0B200_ERR_UNSUPPORTED;
+  if (m == 0) return LC0B200_OK;
+  return linear_int8(out, a, w_nk, col_scale, bias, scratch_q, scratch_scale, m, n, k, activation, S(stream));
 }
 
 LC0B200_API int lc0b200_promotion_logits(void* records, const void* keys, const void* w, int batch_size, int width,

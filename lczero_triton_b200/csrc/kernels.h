@@ -28,6 +28,11 @@ int embed_concat(void* out, const uint64_t* masks, const float* values, const vo
 int quantize_rows(void* out, float* scale, const void* in, long long rows, int width, long long ld_in,
                   cudaStream_t st);
 
+// api.cu: quantise rows into scratch, then the int8 GEMM with the dequantising epilogue.
+int linear_int8(void* out, const void* a, const void* w_nk, const float* col_scale, const void* bias,
+                void* scratch_q, float* scratch_scale, long long m, int n, int k, int activation,
+                cudaStream_t stream);
+
 // layernorm.cu
 int layer_norm(void* out, const void* in, const void* bias, const void* skip, const void* gamma, const void* beta,
                const void* alpha, long long rows, int width, int activation, int has_skip, float epsilon,

@@ -180,6 +180,17 @@ def quantize_rows(out: torch.Tensor, scale: torch.Tensor, x: torch.Tensor, row_c
     return out, scale
 
 
+def linear_int8(out: torch.Tensor, a: torch.Tensor, w_nk: torch.Tensor, col_scale: torch.Tensor,
+                bias: torch.Tensor | None, scratch_q: torch.Tensor, scratch_scale: torch.Tensor, *, m: int, n: int,
+                k: int, activation: str = "none") -> torch.Tensor:
+    """bf16 activations -> per-row int8 (into caller scratch) -> int8 GEMM -> dequant + bias + activation."""
+    _require(a, torch.bfloat16, "a"); _require(w_nk, torch.int8, "w_nk"); _require(scratch_q, torch.int8, "scratch_q")
+    check(_lib.load().lc0b200_linear_int8(_p(out), _p(a), _p(w_nk), _p(col_scale), _p(bias), _p(scratch_q),
+                                          _p(scratch_scale), m, n, k, ACTIVATIONS[activation], _stream()),
+          "linear_int8", launches=2)
+    return out
+
+
 def promotion_logits(records: torch.Tensor, keys: torch.Tensor, w: torch.Tensor, batch_size: int,
                      width: int) -> torch.Tensor:
     check(_lib.load().lc0b200_promotion_logits(_p(records), _p(keys), _p(w), batch_size, width, _stream()),

@@ -151,6 +151,23 @@ def test_int8_gemm_dequant_bias_mish_epilogue(ops) -> None:
     torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=4e-3)
 
 
+@pytest.mark.parametrize(("m", "n", "k"), [(256, 1536, 1024), (100, 1024, 1536), (33, 40, 24)])
+def test_linear_int8_equals_quantise_then_gemm(ops, m, n, k) -> None:
+    a = torch.randn((m, k), generator=_gen(160)).to(BF16)
+    w = (torch.randn((k, n), generator=_gen(161)) * 0.02).to(BF16)
+    bias = (torch.randn(n, generator=_gen(162)) * 0.1).to(BF16)
+    wq, s_w = int8_oracle.quantize_weight(w)
+    want = O.activate(int8_oracle.linear(a, w, bias), "mish")
+    out = torch.empty((m, n), dtype=BF16, device="cuda")
+    scratch_q = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    scratch_s = torch.empty((m,), dtype=torch.float32, device="cuda")
+    ops.linear_int8(out, a.cuda(), wq.t().contiguous().cuda(), s_w.cuda(), bias.cuda(), scratch_q, scratch_s,
+                    m=m, n=n, k=k, activation="mish")
+    torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=4e-3)
+    want_q, want_s = int8_oracle.quantize_rows(a)
+    assert torch.equal(scratch_q.cpu(), want_q) and torch.equal(scratch_s.cpu(), want_s)
+
+
 def test_gemm_linearity_at_full_size(ops) -> None:
     """Size-independent property at the benchmark's row count: GEMM(a1 + a2) = GEMM(a1) + GEMM(a2)
     when the sums are exact in bf16 (small integers), checked on sampled rows of a 262144-row problem."""
