@@ -37,7 +37,8 @@ enum {
   LC0B200_ERR_UNSUPPORTED = 3,
   LC0B200_ERR_MISALIGNED = 4,
   LC0B200_ERR_CUDA = 5,
-  LC0B200_ERR_DEVICE_TIMEOUT = 6
+  LC0B200_ERR_DEVICE_TIMEOUT = 6,
+  LC0B200_ERR_SCRATCH_LIMIT = 7
 };
 
 /* Activation codes (K/add_vectors.py:19-26 has none/mish/relu, K/layer_norm.py:18-25 has
@@ -178,6 +179,26 @@ LC0B200_API int lc0b200_quantize_rows(void* out_int8, float* scale_f32, const vo
 LC0B200_API int lc0b200_linear_int8(void* out_bf16, const void* a_bf16, const void* w_nk_int8, const float* col_scale,
                         const void* bias_bf16, void* scratch_q, float* scratch_scale, long long m, int n, int k,
                         int activation, void* stream);
+
+/* The same layer for callers that cannot allocate device memory at all (no counterpart in the
+ * reference, whose kernels never need temporaries).  Think of an executor that runs a buffer plan
+ * fixed at link time, or a search thread that must not call cudaMalloc because it stalls the whole
+ * device: they pass only the input, the weights and the output, and the quantised activations and
+ * row scales live in an array that is part of the library image.
+ *  - Limits: m <= LC0B200_STATIC_MAX_ROWS and m * k <= LC0B200_STATIC_MAX_ACT_BYTES; anything larger
+ *    is refused with LC0B200_ERR_SCRATCH_LIMIT and nothing is launched.  Every GPU that loads the
+ *    library holds the array (about 8.06 MiB) until the process exits.
+ *  - The first call on each device looks up the array's device address (no allocation); make that
+ *    first call before any stream capture begins on that device.
+ *  - All calls share the one array and it keeps what the last call wrote.  Nothing in it needs
+ *    clearing between calls, but two calls whose kernels overlap on the GPU (different streams,
+ *    or different host threads on the same device) race on it: keep them on one stream.
+ *  - No cudaMalloc, cudaFree or other allocating routine is called, here or below. */
+#define LC0B200_STATIC_MAX_ROWS 16384
+#define LC0B200_STATIC_MAX_ACT_BYTES (8 * 1024 * 1024)
+LC0B200_API int lc0b200_linear_int8_static(void* out_bf16, const void* a_bf16, const void* w_nk_int8,
+                               const float* col_scale, const void* bias_bf16, long long m, int n, int k,
+                               int activation, void* stream);
 
 /* ---- heads -------------------------------------------------------------------------------- */
 

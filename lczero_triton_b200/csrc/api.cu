@@ -73,6 +73,7 @@ LC0B200_API const char* lc0b200_status_string(int status) {
     case LC0B200_ERR_MISALIGNED: return "misaligned pointer or pitch";
     case LC0B200_ERR_CUDA: return "CUDA error";
     case LC0B200_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case LC0B200_ERR_SCRATCH_LIMIT: return "problem exceeds the built-in scratch array";
     default: return "unknown status";
   }
 }

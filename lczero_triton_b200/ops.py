@@ -191,6 +191,18 @@ def linear_int8(out: torch.Tensor, a: torch.Tensor, w_nk: torch.Tensor, col_scal
     return out
 
 
+def linear_int8_static(out: torch.Tensor, a: torch.Tensor, w_nk: torch.Tensor, col_scale: torch.Tensor,
+                       bias: torch.Tensor | None, *, m: int, n: int, k: int, activation: str = "none") -> torch.Tensor:
+    """``linear_int8`` for callers that cannot allocate: the quantised activations and row scales
+    go to an array built into the library (limits in ``include/lc0b200.h``), so only the input,
+    the weights and the output are passed.  Calls share that array; keep them on one stream."""
+    _require(a, torch.bfloat16, "a"); _require(w_nk, torch.int8, "w_nk")
+    check(_lib.load().lc0b200_linear_int8_static(_p(out), _p(a), _p(w_nk), _p(col_scale), _p(bias), m, n, k,
+                                                 ACTIVATIONS[activation], _stream()),
+          "linear_int8_static", launches=2)
+    return out
+
+
 def promotion_logits(records: torch.Tensor, keys: torch.Tensor, w: torch.Tensor, batch_size: int,
                      width: int) -> torch.Tensor:
     check(_lib.load().lc0b200_promotion_logits(_p(records), _p(keys), _p(w), batch_size, width, _stream()),
