@@ -3,7 +3,12 @@
 // (bt4/kernels/matmul.py:57-116) and, through the fused epilogue, the bias/activation kernels
 // that follow it in the graph (bt4/kernels/add_bias_batched.py, add_vectors.py).
 //
-// One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
+// One persistent CTA per SM walks output tiles of 128 x BN; for the large GEMMs two CTAs on the
+// two SMs of a TPC form a cluster and share 256 x 256 tiles (tcgen05 cta_group::2: each CTA stages
+// its own 128 rows of A and its own half of the weight tile, the leader CTA issues MMAs that read
+// both shared memories, each CTA's TMEM receives its 128 rows of the accumulator).  That halves the
+// weight traffic per CTA and deepens the pipeline from 4 to 6 stages.  No load is multicast: every
+// CTA fetches its own operands with plain per-CTA TMA.  Warp roles:
 //   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one elected lane issues tcgen05.mma; owns the TMEM allocation)
 //   warps 2..    epilogue      (tcgen05.ld -> bias / dequant / activation -> bf16 -> swizzled
@@ -17,6 +22,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm.h"
 #include "ptx.cuh"
@@ -29,19 +36,23 @@ constexpr int kBM = 128;          // tile rows = TMEM lanes
 constexpr int kRowBytes = 128;    // one swizzle row: 64 bf16 or 128 int8 along K
 constexpr int kStagingBytesPerWarp = 32 * kRowBytes;  // 32 rows x 64 bf16 columns
 
-template <int BN>
+template <int BN, int CTAS>
 struct TileCfg {
+  static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
   static constexpr int kABytes = kBM * kRowBytes;
-  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kBRows = BN / CTAS;          // weight-tile rows (N) staged by each CTA
+  static constexpr int kBBytes = kBRows * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // Keep below the 227 KB per-CTA limit with room for barriers and 1 KB alignment slack.
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
   static constexpr int kEpilogueWarps = (BN >= 128) ? 8 : 4;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
   static constexpr bool kTmaStore = BN >= 128;  // each epilogue warp then owns at least one 64-column group
   static constexpr int kStagingBytes = kTmaStore ? kEpilogueWarps * kStagingBytesPerWarp : 0;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+  // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
+  static constexpr int kFit = (227 * 1024 - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
 };
 
 struct KernelParams {
@@ -128,19 +139,20 @@ __device__ __forceinline__ void finish_chunk_bf16(const uint32_t (&v)[32], uint3
   for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
 }
 
-template <int BN, bool INT8, bool W_KN>
-__global__ void __launch_bounds__(TileCfg<BN>::kThreads, 1)
+template <int BN, bool INT8, bool W_KN, int CTAS>
+__global__ void __launch_bounds__(TileCfg<BN, CTAS>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const KernelParams p) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, CTAS>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
   constexpr int kUmmaK = INT8 ? 32 : 16;          // K per tcgen05.mma (32 bytes)
   constexpr int kMmaPerStage = kElemsPerRow / kUmmaK;  // 4
   constexpr int kPanelN = INT8 ? 128 : 64;        // N elements per 128-byte row (MN-major weight staging)
-  constexpr int kPanels = (BN + kPanelN - 1) / kPanelN;
+  constexpr int kPanels = (Cfg::kBRows + kPanelN - 1) / kPanelN;
   constexpr int kPanelBytes = kElemsPerRow * kRowBytes;  // K rows x 128 B
-  static_assert(!W_KN || (BN % kPanelN == 0), "MN-major weight staging needs whole 128-byte panels");
+  constexpr int kTileM = kBM * CTAS;              // rows of C per tile (per CTA pair when CTAS == 2)
+  static_assert(!W_KN || (Cfg::kBRows % kPanelN == 0), "MN-major weight staging needs whole 128-byte panels");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -148,18 +160,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t smem_b = smem_base + kStages * Cfg::kABytes;
   const uint32_t staging_base = smem_base + kStages * Cfg::kStageBytes;  // 1024-byte aligned
   const uint32_t bar_base = staging_base + Cfg::kStagingBytes;
-  const uint32_t bar_full = bar_base;                   // [kStages]
+  const uint32_t bar_full = bar_base;                   // [kStages]  (used in the leader CTA only)
   const uint32_t bar_empty = bar_base + 8 * kStages;    // [kStages]
   const uint32_t bar_acc_full = bar_base + 16 * kStages;       // [2]
-  const uint32_t bar_acc_empty = bar_base + 16 * kStages + 16; // [2]
+  const uint32_t bar_acc_empty = bar_base + 16 * kStages + 16; // [2]  (used in the leader CTA only)
   const uint32_t tmem_slot = bar_base + 16 * kStages + 32;
   __shared__ int abort_flag_storage;
   volatile int* abort_flag = &abort_flag_storage;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Rank inside the CTA pair: rank 0 is the leader (issues the MMAs, owns the full / acc-empty barriers).
+  const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+  const uint32_t group = blockIdx.x / CTAS;       // CTA pair (or CTA) index
+  const uint32_t num_groups = gridDim.x / CTAS;
 
-  const long long m_tiles = (p.m + kBM - 1) / kBM;
+  const long long m_tiles = (p.m + kTileM - 1) / kTileM;
   const int n_tiles = (p.n + BN - 1) / BN;
   const long long num_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.k + kElemsPerRow - 1) / kElemsPerRow;
@@ -172,7 +188,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(bar_acc_full + 8 * a, 1);
-      ptx::mbar_init(bar_acc_empty + 8 * a, Cfg::kEpilogueWarps);
+      ptx::mbar_init(bar_acc_empty + 8 * a, Cfg::kEpilogueWarps * CTAS);
     }
     ptx::mbar_init_fence();
     ptx::prefetch_tensormap(&map_a);
@@ -180,39 +196,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (p.tma_store) ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    ptx::tmem_relinquish();
+    if (CTAS == 2) {
+      ptx::tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (CTAS == 2) ptx::cluster_sync();  // the peer's barriers exist before anything signals them
   ptx::tc_fence_after_sync();
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (every CTA loads its own operands)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = static_cast<int>(tile / n_tiles) * kBM;
-        const int n0 = static_cast<int>(tile % n_tiles) * BN;
+      for (long long tile = group; tile < num_tiles && ok; tile += num_groups) {
+        const int m0 = static_cast<int>(tile / n_tiles) * kTileM + static_cast<int>(rank) * kBM;
+        const int n0 = static_cast<int>(tile % n_tiles) * BN + static_cast<int>(rank) * Cfg::kBRows;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
           if (!ok) break;
-          const uint32_t full = bar_full + 8 * stage;
-          ptx::mbar_expect_tx(full, Cfg::kStageBytes);
+          // Transaction bytes of both CTAs complete on the leader's barrier.
+          const uint32_t full = (CTAS == 2) ? ptx::map_to_cta(bar_full + 8 * stage, 0u) : bar_full + 8 * stage;
+          if (rank == 0) ptx::mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes * CTAS);
           const int k0 = kb * kElemsPerRow;
-          ptx::tma_load_2d(smem_a + stage * Cfg::kABytes, &map_a, k0, m0, full);
+          ptx::tma_load_2d<CTAS>(smem_a + stage * Cfg::kABytes, &map_a, k0, m0, full);
           if (W_KN) {
 #pragma unroll
             for (int pnl = 0; pnl < kPanels; ++pnl) {
-              ptx::tma_load_2d(smem_b + stage * Cfg::kBBytes + pnl * kPanelBytes, &map_w, n0 + pnl * kPanelN, k0,
-                               full);
+              ptx::tma_load_2d<CTAS>(smem_b + stage * Cfg::kBBytes + pnl * kPanelBytes, &map_w, n0 + pnl * kPanelN,
+                                     k0, full);
             }
           } else {
-            ptx::tma_load_2d(smem_b + stage * Cfg::kBBytes, &map_w, k0, n0, full);
+            ptx::tma_load_2d<CTAS>(smem_b + stage * Cfg::kBBytes, &map_w, k0, n0, full);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -223,15 +246,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc =
-          ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kBM), static_cast<uint32_t>(BN));
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kTileM),
+                                                 static_cast<uint32_t>(BN));
       int stage = 0;
       uint32_t phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         ok = ptx::mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 0x200u + acc);
@@ -253,20 +276,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint64_t db = W_KN ? ptx::smem_desc_sw128(b_addr + j * kUmmaK * kRowBytes, kPanelBytes, 1024)
                                      : ptx::smem_desc_sw128(b_addr + j * 32, 16, 1024);
             const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
-            if (INT8) {
-              ptx::mma_i8(tmem_d, da, db, idesc, accumulate);
-            } else {
-              ptx::mma_bf16(tmem_d, da, db, idesc, accumulate);
-            }
+            ptx::mma<INT8, CTAS>(tmem_d, da, db, idesc, accumulate);
           }
-          ptx::tc_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
+          // Free the smem stage (in both CTAs) once these MMAs have read it.
+          ptx::tc_commit<CTAS>(bar_empty + 8 * stage);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        ptx::tc_commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
+        ptx::tc_commit<CTAS>(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue (both CTAs)
       }
     }
     __syncwarp();
@@ -281,8 +301,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;
     uint32_t local = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      const long long m0 = (tile / n_tiles) * kBM;
+    for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
+      const long long m0 = (tile / n_tiles) * kTileM + rank * kBM;
       const int n0 = static_cast<int>(tile % n_tiles) * BN + half * kColsPerWarp;
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
@@ -384,7 +404,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // TMEM has been read out: hand the accumulator back before the stores drain.
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+      if (lane == 0) {
+        if (CTAS == 2) {
+          ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_acc_empty + 8 * acc, 0u));  // the leader's barrier
+        } else {
+          ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+        }
+      }
     }
     if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
@@ -393,13 +419,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // ------------------------------------------------------------ teardown
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // Neither CTA of a pair may leave while the other can still signal its barriers or read its smem.
+  if (CTAS == 2) ptx::cluster_sync();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (CTAS == 2) {
+      ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    } else {
+      ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
   }
 }
 
 // ---------------------------------------------------------------- host side
+
+// LC0B200_GEMM_PAIRS=0 in the environment keeps every GEMM on the single-CTA kernel (measurement aid).
+bool pair_kernels_enabled() {
+  static const bool enabled = []() {
+    const char* v = getenv("LC0B200_GEMM_PAIRS");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return enabled;
+}
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -435,9 +476,9 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool INT8, bool W_KN>
+template <int BN, bool INT8, bool W_KN, int CTAS>
 int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, CTAS>;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;
   constexpr int kPanelN = INT8 ? 128 : 64;
   const int eb = INT8 ? 1 : 2;
@@ -446,14 +487,14 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   if (W_KN) {
     if (!make_map(&map_w, g.w, eb, g.k, g.n, g.ldw, kElemsPerRow, kPanelN)) return LC0B200_ERR_CUDA;
   } else {
-    if (!make_map(&map_w, g.w, eb, g.n, g.k, g.ldw, BN, kElemsPerRow)) return LC0B200_ERR_CUDA;
+    if (!make_map(&map_w, g.w, eb, g.n, g.k, g.ldw, Cfg::kBRows, kElemsPerRow)) return LC0B200_ERR_CUDA;
   }
-  const int out_eb_probe = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
+  const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
   const bool tma_store = Cfg::kTmaStore && g.out_kind == LC0B200_OUT_BF16 && aligned16(g.out) &&
-                         ((g.ldc * out_eb_probe) % 16 == 0);
+                         ((g.ldc * out_eb) % 16 == 0);
   CUtensorMap map_out = map_a;  // placeholder when the direct-store epilogue is used
   if (tma_store && !make_map(&map_out, g.out, 2, g.m, g.n, g.ldc, 32, 64)) return LC0B200_ERR_CUDA;
-  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN>;
+  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -474,30 +515,49 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   p.activation = g.activation;
   p.status = device_status_words();
   if (p.status == nullptr) return LC0B200_ERR_CUDA;
-  const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
   p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16)) &&
              (g.col_scale == nullptr || aligned16(g.col_scale));
   p.tma_store = tma_store ? 1 : 0;
-  const long long tiles = ceil_div_ll(g.m, kBM) * ceil_div_ll(g.n, BN);
-  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, map_out, p);
+  const long long tiles = ceil_div_ll(g.m, kBM * CTAS) * ceil_div_ll(g.n, BN);
+  const long long max_groups = sm_count() / CTAS;
+  const unsigned grid = static_cast<unsigned>((tiles < max_groups ? tiles : max_groups) * CTAS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CTAS == 2 ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, p) != cudaSuccess) return LC0B200_ERR_CUDA;
   return launch_status();
 }
+
+// Rows at and above which the 256-wide tiles are shared by CTA pairs (below it there are too few
+// 256 x 256 tiles to fill 74 pairs and the single-CTA kernel balances better).
+constexpr long long kPairMinRows = 8192;
 
 template <bool INT8, bool W_KN>
 int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   // MN-major weight staging needs BN to be a whole number of 128-byte panels
   // (64 bf16 or 128 int8 columns); narrower outputs just run a partly empty tile.
   constexpr int kMinBn = W_KN ? (INT8 ? 128 : 64) : 32;
-  if (g.n > 128) return launch<256, INT8, W_KN>(g, stream);
+  if (g.n > 128) {
+    if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2>(g, stream);
+    return launch<256, INT8, W_KN, 1>(g, stream);
+  }
   if constexpr (kMinBn <= 128) {
-    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN>(g, stream);
+    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN, 1>(g, stream);
   }
   if constexpr (kMinBn <= 64) {
-    if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN>(g, stream);
+    if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN, 1>(g, stream);
   }
   if constexpr (kMinBn <= 32) {
-    return launch<32, INT8, W_KN>(g, stream);
+    return launch<32, INT8, W_KN, 1>(g, stream);
   }
   return LC0B200_ERR_UNSUPPORTED;
 }

@@ -55,6 +55,8 @@ SHAPES = [
     (128, 256, 64), (128, 256, 1024), (256, 1024, 1024), (1024, 1536, 1024), (640, 1024, 1536),
     (512, 3072, 1024), (300, 1000, 520), (64, 32768, 768), (4096, 32, 1024), (4096, 16, 128),
     (77, 64, 2048), (130, 128, 8192), (2048, 4096, 256), (33, 8192, 256), (1000, 1024, 624), (5, 128, 128),
+    # 8192 rows and more with a wide output: 256 x 256 tiles shared by CTA pairs
+    (8200, 1536, 1024), (16384, 3072, 1024), (8192, 1000, 520), (9000, 4096, 256),
 ]
 
 
@@ -114,7 +116,7 @@ def test_reference_layout_matmul_on_unaligned_shapes(ops, m, n, k) -> None:
 
 
 @pytest.mark.parametrize(("m", "n", "k"), [(128, 256, 128), (300, 1000, 528), (1024, 3072, 1024), (512, 1024, 1536),
-                                            (64, 128, 4096), (4096, 32, 1024)])
+                                            (64, 128, 4096), (4096, 32, 1024), (8200, 1024, 1536), (16384, 1536, 1024)])
 @pytest.mark.parametrize("layout", ["nk", "kn"])
 def test_int8_gemm_accumulators_are_bit_exact(ops, m, n, k, layout) -> None:
     from lczero_triton_b200 import _lib
