@@ -345,8 +345,24 @@ def run_kernel(args) -> None:
         act = "mish" if args.epilogue == "bias_mish" else "none"
         layout = _lib.W_NK if args.layout == "nk" else _lib.W_KN
 
+        extra = {}
+        if args.epilogue in ("res", "res_ln"):  # residual epilogue: z = alpha * (acc + b) + (LN of) skip, with row sums
+            bias = torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16)
+            extra = {"res_skip": torch.randn((m, n), generator=gen, device="cuda").to(torch.bfloat16), "res_alpha": 0.43,
+                     "stats_out": torch.empty(((n + 63) // 64, m, 2), dtype=torch.float32, device="cuda")}
+            if args.epilogue == "res_ln":
+                extra["res_ln"] = (torch.rand(((n + 63) // 64, m, 2), generator=gen, device="cuda") + 1.0,
+                                   torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16),
+                                   torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16))
+        elif args.epilogue in ("ln_in", "ln_in_mish"):  # LayerNorm of the A rows folded into the epilogue
+            bias = None
+            extra = {"ln_in": (torch.rand(((k + 63) // 64, m, 2), generator=gen, device="cuda") + 1.0,
+                               torch.randn(n, generator=gen, device="cuda"), torch.randn(n, generator=gen, device="cuda"))}
+            act = "mish" if args.epilogue == "ln_in_mish" else "none"
+
         def once() -> None:
-            ops.gemm(out, a, w, m=m, n=n, k=k, bias=bias, activation=act, w_layout=layout, row_scale=rs, col_scale=cs)
+            ops.gemm(out, a, w, m=m, n=n, k=k, bias=bias, activation=act, w_layout=layout, row_scale=rs, col_scale=cs,
+                     **extra)
 
         ms = _timed_steps(once, 3, args.iters, None) / args.iters
         achieved = 2.0 * m * n * k / (ms * 1e-3) / 1e12
@@ -410,7 +426,8 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--layout", default="nk", choices=["nk", "kn"])
-    ap.add_argument("--epilogue", default="bias", choices=["none", "bias", "bias_mish"])
+    ap.add_argument("--epilogue", default="bias",
+                    choices=["none", "bias", "bias_mish", "res", "res_ln", "ln_in", "ln_in_mish"])
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32", "s32"])
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--width", type=int, default=1024)

@@ -137,6 +137,32 @@ typedef struct lc0b200_gemm_args {
   int out_kind;  /* LC0B200_OUT_* */
   int w_layout;  /* LC0B200_W_*   */
   int activation;
+  /* ---- deferred LayerNorm (all zero = off).  The residual stream can be kept as the PRE-normalisation
+   * rows z plus per-row partial sums, so that the stand-alone LayerNorm launches
+   * (K/layer_norm.py:37-161, two per encoder layer) disappear:
+   *   producer ("res"):  y = res_alpha * (acc + bias[n]) + skip[m,n], stored as bf16, and
+   *     stats_out[part][m] = (sum, sum of squares) of the stored values over output columns
+   *     [64*part, 64*part+64), part < ceil(n/64).  skip is plain bf16, or, when res_stats is given,
+   *     itself deferred: skip = (z[m,n] - mean[m]) * rstd[m] * res_gamma[n] + res_beta[n] with mean /
+   *     rstd from res_stats ([res_parts][m] partials over a width of n).
+   *   consumer ("ln_in"): A holds deferred rows; with W' = diag(gamma) W staged as the weight,
+   *     ln_in_c[n] = sum_k W'[k,n] and ln_in_d[n] = sum_k beta[k] W[k,n] + bias[n]:
+   *     y = rstd[m] * (acc - mean[m] * ln_in_c[n]) + ln_in_d[n]   (bias_bf16 is ignored), then the
+   *     activation.  mean / rstd come from ln_in_stats ([ln_in_parts][m] partials over a width of k).
+   * Both need a bf16 output with a 16-byte aligned base and pitch and n > 64. */
+  const float* ln_in_stats;
+  const float* ln_in_c;
+  const float* ln_in_d;
+  int ln_in_parts;
+  float ln_eps;
+  const void* res_skip_bf16;
+  long long ld_skip;
+  const float* res_stats;
+  const void* res_gamma_bf16;
+  const void* res_beta_bf16;
+  int res_parts;
+  float res_alpha;
+  float* stats_out;
 } lc0b200_gemm_args;
 LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* args_host, void* stream);
 /* Same contract on the plain CUDA-core kernel (any shape / alignment; used for the tiny head

@@ -31,6 +31,11 @@ class GemmArgs(ctypes.Structure):
         ("m", c_longlong), ("n", c_int), ("k", c_int),
         ("lda", c_longlong), ("ldw", c_longlong), ("ldc", c_longlong),
         ("in_type", c_int), ("out_kind", c_int), ("w_layout", c_int), ("activation", c_int),
+        ("ln_in_stats", c_void_p), ("ln_in_c", c_void_p), ("ln_in_d", c_void_p),
+        ("ln_in_parts", c_int), ("ln_eps", c_float),
+        ("res_skip_bf16", c_void_p), ("ld_skip", c_longlong), ("res_stats", c_void_p),
+        ("res_gamma_bf16", c_void_p), ("res_beta_bf16", c_void_p), ("res_parts", c_int), ("res_alpha", c_float),
+        ("stats_out", c_void_p),
     ]
 
 

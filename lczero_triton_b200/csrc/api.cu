@@ -172,7 +172,20 @@ static int check_gemm(const lc0b200_gemm_args* g) {
   if (g->w_layout != LC0B200_W_KN && g->w_layout != LC0B200_W_NK) return LC0B200_ERR_UNSUPPORTED;
   if (!valid_activation(g->activation)) return LC0B200_ERR_UNSUPPORTED;
   if (g->out_kind == LC0B200_OUT_S32 && g->in_type != LC0B200_IN_INT8) return LC0B200_ERR_UNSUPPORTED;
+  if (g->ln_in_stats != nullptr) {
+    REQUIRE_PTR(g->ln_in_c); REQUIRE_PTR(g->ln_in_d);
+    REQUIRE_SHAPE(g->ln_in_parts > 0);
+  }
+  if (g->res_stats != nullptr) {
+    REQUIRE_PTR(g->res_skip_bf16); REQUIRE_PTR(g->res_gamma_bf16); REQUIRE_PTR(g->res_beta_bf16);
+    REQUIRE_SHAPE(g->res_parts > 0);
+  }
+  if (g->res_skip_bf16 != nullptr) REQUIRE_SHAPE(g->ld_skip >= g->n);
   return LC0B200_OK;
+}
+
+static bool has_deferred_layer_norm(const lc0b200_gemm_args* g) {
+  return g->ln_in_stats != nullptr || g->res_skip_bf16 != nullptr || g->stats_out != nullptr;
 }
 
 LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* g, void* stream) {
@@ -180,6 +193,7 @@ LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* g, void* stream) {
   if (st != LC0B200_OK) return st;
   if (g->m == 0) return LC0B200_OK;
   if (gemm_tcgen05_supported(*g)) return gemm_tcgen05(*g, S(stream));
+  if (has_deferred_layer_norm(g)) return LC0B200_ERR_UNSUPPORTED;
   return gemm_simt(*g, S(stream));
 }
 
@@ -187,6 +201,7 @@ LC0B200_API int lc0b200_gemm_simt(const lc0b200_gemm_args* g, void* stream) {
   const int st = check_gemm(g);
   if (st != LC0B200_OK) return st;
   if (g->m == 0) return LC0B200_OK;
+  if (has_deferred_layer_norm(g)) return LC0B200_ERR_UNSUPPORTED;
   return gemm_simt(*g, S(stream));
 }
 

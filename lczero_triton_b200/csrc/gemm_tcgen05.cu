@@ -1,24 +1,27 @@
 // Tensor-core GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with the
 // accumulator in TMEM, fused epilogue.  Replaces the reference's Triton _matmul_kernel
 // (bt4/kernels/matmul.py:57-116) and, through the fused epilogue, the bias/activation kernels
-// that follow it in the graph (bt4/kernels/add_bias_batched.py, add_vectors.py).
+// that follow it in the graph (bt4/kernels/add_bias_batched.py, add_vectors.py) and the
+// LayerNorm launches (bt4/kernels/layer_norm.py) via the deferred-LayerNorm epilogues.
 //
 // One persistent CTA per SM walks output tiles of 128 x BN; for the large GEMMs two CTAs on the
 // two SMs of a TPC form a cluster and share 256 x 256 tiles (tcgen05 cta_group::2: each CTA stages
 // its own 128 rows of A and its own half of the weight tile, the leader CTA issues MMAs that read
-// both shared memories, each CTA's TMEM receives its 128 rows of the accumulator).  That halves the
-// weight traffic per CTA and deepens the pipeline from 4 to 6 stages.  No load is multicast: every
-// CTA fetches its own operands with plain per-CTA TMA.  Warp roles:
+// both shared memories, each CTA's TMEM receives its 128 rows of the accumulator).  No load is
+// multicast: every CTA fetches its own operands with plain per-CTA TMA.  Warp roles:
 //   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one elected lane issues tcgen05.mma; owns the TMEM allocation)
-//   warps 2..    epilogue      (tcgen05.ld -> bias / dequant / activation -> bf16 -> swizzled
-//                              shared-memory staging -> TMA store; eight warps for BN >= 128:
-//                              two per TMEM lane quarter, each taking half of the columns)
-// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
-// overlaps the main loop of tile i+1.  bf16 results leave through cp.async.bulk.tensor stores
-// (full 128-byte lines, clipped at the matrix edge by the tensor map); f32 / raw s32 results and
-// unaligned outputs use direct stores.  Operands are staged K-major with the 128-byte swizzle;
-// the weight operand may instead be staged MN-major straight from the reference's [K,N] layout.
+//   warps 2..   epilogue       (eight warps for BN >= 128: two per TMEM lane quarter, each taking
+//                               half of the tile's columns in groups of 64)
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
+// main loop of tile i+1.  The epilogue is organised so that nothing it needs from global memory is
+// on the critical path after the accumulator arrives: per-row LayerNorm statistics are read while
+// the tile is still being multiplied, the residual operand of a 32 x 64 group is brought into the
+// warp's swizzled staging buffer by TMA ahead of time, the result overwrites it in place and leaves
+// through a TMA store (full 128-byte lines, clipped at the matrix edge by the tensor map).
+// f32 / raw s32 results, narrow tiles and unaligned outputs use direct stores.  Operands are staged
+// K-major with the 128-byte swizzle; the weight operand may instead be staged MN-major straight from
+// the reference's [K,N] layout.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -32,11 +35,17 @@ namespace lc0b200 {
 
 namespace {
 
-constexpr int kBM = 128;          // tile rows = TMEM lanes
+constexpr int kBM = 128;          // tile rows per CTA = TMEM lanes
 constexpr int kRowBytes = 128;    // one swizzle row: 64 bf16 or 128 int8 along K
-constexpr int kStagingBytesPerWarp = 32 * kRowBytes;  // 32 rows x 64 bf16 columns
+constexpr int kGroupBytes = 32 * kRowBytes;  // staging for 32 rows x 64 bf16 columns
 
-template <int BN, int CTAS>
+// Epilogue flavours (compile-time, so that the hot loop carries no dead code):
+//   kPlain: y = act(dequant(acc) + bias)
+//   kLnIn : y = act(rstd[m] * (acc - mean[m] * c[n]) + d[n])        LayerNorm of the A rows folded in
+//   kRes  : y = alpha * (dequant(acc) + bias) + skip, skip plain or a deferred LayerNorm; row sums out
+enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
+
+template <int BN, int CTAS, int MODE>
 struct TileCfg {
   static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
   static constexpr int kABytes = kBM * kRowBytes;
@@ -46,12 +55,18 @@ struct TileCfg {
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
   static constexpr int kEpilogueWarps = (BN >= 128) ? 8 : 4;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-  static constexpr bool kTmaStore = BN >= 128;  // each epilogue warp then owns at least one 64-column group
-  static constexpr int kStagingBytes = kTmaStore ? kEpilogueWarps * kStagingBytesPerWarp : 0;
-  static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr bool kTmaStore = BN >= 128;      // each epilogue warp then owns whole 64-column groups
+  static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
+  static constexpr int kGroups = kColsPerWarp / 64; // 64-column groups per warp and tile (TMA-store path)
+  // Staging buffers per warp: one, reused group after group; the residual flavour keeps one per
+  // group because the skip operand of the whole tile is prefetched into them.
+  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : (MODE == kRes ? kGroups : 1);
+  static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
+  static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 512 /*barriers*/;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
   static constexpr int kFit = (227 * 1024 - kFixedBytes) / kStageBytes;
   static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  static_assert(kStages >= 3, "pipeline too shallow");
   static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
 };
 
@@ -66,63 +81,152 @@ struct KernelParams {
   int k;
   int out_kind;
   int activation;
-  int vec_ok;     // out / bias / col_scale are 16-byte aligned and ldc keeps rows aligned
+  int vec_ok;     // out / bias / scales / fold vectors are 16-byte aligned and ldc keeps rows aligned
   int tma_store;  // bf16 output that a tensor map can address (map_out is valid)
   unsigned int* status;
+  // Deferred LayerNorm (see lc0b200_gemm_args).
+  const float2* ln_in_stats;
+  const float* ln_in_c;
+  const float* ln_in_d;
+  int ln_in_parts;
+  float ln_in_inv_width;
+  float ln_eps;
+  const bf16* res_skip;
+  long long ld_skip;
+  const float2* res_stats;
+  const bf16* res_gamma;
+  const bf16* res_beta;
+  int res_parts;
+  float res_inv_width;
+  float res_alpha;
+  float2* stats_out;
 };
 
-template <bool INT8>
-__device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* __restrict__ cs, int col) {
-  if (INT8) {
-    float y = static_cast<float>(static_cast<int>(raw)) * rs;
-    return cs != nullptr ? y * __ldg(cs + col) : y;
+// Per-thread (= per output row) values the epilogue needs.
+struct RowCtx {
+  float rs;       // int8: activation scale of this row
+  float mean;     // kLnIn: mean and 1/sqrt(var + eps) of this row of A;  kRes: of this row of the skip operand
+  float rstd;
+  bool row_ok;
+};
+
+__device__ __forceinline__ void row_stats(const float2* stats, int parts, long long m, long long row, float inv_width,
+                                          float eps, float& mean, float& rstd) {
+  float s = 0.0f, q = 0.0f;
+  for (int i = 0; i < parts; ++i) {
+    const float2 t = __ldg(stats + i * m + row);
+    s += t.x;
+    q += t.y;
   }
-  return __uint_as_float(raw);
+  mean = s * inv_width;
+  const float var = fmaxf(q * inv_width - mean * mean, 0.0f);
+  rstd = rsqrtf(var + eps);
 }
 
-// One 32-column chunk of one accumulator row: dequantise, add bias, activate, pack to bf16.
-template <bool INT8>
-__device__ __forceinline__ void finish_chunk_bf16(const uint32_t (&v)[32], uint32_t (&packed)[16], int col0, float rs,
-                                                  const KernelParams& p) {
-  const bool vec = p.vec_ok && (col0 + 32 <= p.n);
-  float b[32], cs[32];
-  if (vec) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint4 braw = make_uint4(0u, 0u, 0u, 0u);
-      if (p.bias != nullptr) braw = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
-      float2 t;
-      t = unpack_bf16x2(braw.x); b[g * 8 + 0] = t.x; b[g * 8 + 1] = t.y;
-      t = unpack_bf16x2(braw.y); b[g * 8 + 2] = t.x; b[g * 8 + 3] = t.y;
-      t = unpack_bf16x2(braw.z); b[g * 8 + 4] = t.x; b[g * 8 + 5] = t.y;
-      t = unpack_bf16x2(braw.w); b[g * 8 + 6] = t.x; b[g * 8 + 7] = t.y;
-    }
-    if (INT8) {
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        float4 c = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (p.col_scale != nullptr) c = __ldg(reinterpret_cast<const float4*>(p.col_scale + col0 + g * 4));
-        cs[g * 4 + 0] = c.x; cs[g * 4 + 1] = c.y; cs[g * 4 + 2] = c.z; cs[g * 4 + 3] = c.w;
-      }
-    }
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  float2 t;
+  t = unpack_bf16x2(raw.x); f[0] = t.x; f[1] = t.y;
+  t = unpack_bf16x2(raw.y); f[2] = t.x; f[3] = t.y;
+  t = unpack_bf16x2(raw.z); f[4] = t.x; f[5] = t.y;
+  t = unpack_bf16x2(raw.w); f[6] = t.x; f[7] = t.y;
+}
+
+template <bool VEC>
+__device__ __forceinline__ void load8_bf16(const bf16* ptr, int valid, float (&f)[8]) {
+  if (VEC) {
+    unpack8(__ldg(reinterpret_cast<const uint4*>(ptr)), f);
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const bool in = col0 + j < p.n;
-      b[j] = (in && p.bias != nullptr) ? __bfloat162float(p.bias[col0 + j]) : 0.0f;
-      if (INT8) cs[j] = (in && p.col_scale != nullptr) ? p.col_scale[col0 + j] : 1.0f;
-    }
+    for (int j = 0; j < 8; ++j) f[j] = j < valid ? __bfloat162float(ptr[j]) : 0.0f;
   }
+}
+
+template <bool VEC>
+__device__ __forceinline__ void load8_f32(const float* ptr, int valid, float fill, float (&f)[8]) {
+  if (VEC) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(ptr));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(ptr) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = j < valid ? ptr[j] : fill;
+  }
+}
+
+// 32 output columns of one row: from raw accumulator words to packed bf16, plus the row's partial
+// sums of what is stored.  `skip` holds the 32 skip values as packed bf16 pairs (kRes).  VEC selects
+// 16-byte loads of the per-column vectors (whole, aligned groups) or guarded scalar loads (matrix
+// edge, odd alignment).  The work is laid out as whole-chunk phases, each over 32 independent
+// values, so that loads are issued together and the transcendental pipe sees long independent runs.
+template <int MODE, bool INT8, bool VEC>
+__device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, int col0, const uint32_t* skip,
+                                         const RowCtx& r, const KernelParams& p, float& sum, float& sumsq) {
   float y[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    float x;
-    if (INT8) {
-      x = (static_cast<float>(static_cast<int>(v[j])) * rs) * cs[j];
-    } else {
-      x = __uint_as_float(v[j]);
+    y[j] = INT8 ? static_cast<float>(static_cast<int>(v[j])) * r.rs : __uint_as_float(v[j]);
+  }
+  if (INT8) {
+    if (p.col_scale != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float cs[8];
+        load8_f32<VEC>(p.col_scale + col0 + g * 8, p.n - col0 - g * 8, 1.0f, cs);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[g * 8 + j] *= cs[j];
+      }
     }
-    y[j] = x + b[j];
+  }
+  if (MODE == kLnIn) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float c[8];
+      load8_f32<VEC>(p.ln_in_c + col0 + g * 8, p.n - col0 - g * 8, 0.0f, c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[g * 8 + j] = r.rstd * (y[g * 8 + j] - r.mean * c[j]);
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float d[8];
+      load8_f32<VEC>(p.ln_in_d + col0 + g * 8, p.n - col0 - g * 8, 0.0f, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[g * 8 + j] += d[j];
+    }
+  } else if (p.bias != nullptr) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float b[8];
+      load8_bf16<VEC>(p.bias + col0 + g * 8, p.n - col0 - g * 8, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[g * 8 + j] += b[j];
+    }
+  }
+  if (MODE == kRes) {
+    float t[32];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = unpack_bf16x2(skip[j]);
+      t[2 * j] = f.x;
+      t[2 * j + 1] = f.y;
+    }
+    if (p.res_stats != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float ga[8];
+        load8_bf16<VEC>(p.res_gamma + col0 + g * 8, p.n - col0 - g * 8, ga);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[g * 8 + j] = (t[g * 8 + j] - r.mean) * r.rstd * ga[j];
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float be[8];
+        load8_bf16<VEC>(p.res_beta + col0 + g * 8, p.n - col0 - g * 8, be);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[g * 8 + j] += be[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = p.res_alpha * y[j] + t[j];
   }
   // The activation code is uniform for the launch: branch once per chunk, not per element.
   if (p.activation == LC0B200_ACT_MISH) {
@@ -137,13 +241,34 @@ __device__ __forceinline__ void finish_chunk_bf16(const uint32_t (&v)[32], uint3
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
+  if (MODE == kRes) {
+    if (p.stats_out != nullptr) {
+      const int valid = VEC ? 32 : p.n - col0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 f = unpack_bf16x2(packed[j]);  // what the consumer will read
+        if (2 * j < valid) { sum += f.x; sumsq += f.x * f.x; }
+        if (2 * j + 1 < valid) { sum += f.y; sumsq += f.y * f.y; }
+      }
+    }
+  }
 }
 
-template <int BN, bool INT8, bool W_KN, int CTAS>
-__global__ void __launch_bounds__(TileCfg<BN, CTAS>::kThreads, 1)
+template <bool INT8>
+__device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* __restrict__ cs, int col) {
+  if (INT8) {
+    float y = static_cast<float>(static_cast<int>(raw)) * rs;
+    return cs != nullptr ? y * __ldg(cs + col) : y;
+  }
+  return __uint_as_float(raw);
+}
+
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
+__global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_out, const KernelParams p) {
-  using Cfg = TileCfg<BN, CTAS>;
+                    const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_skip,
+                    const KernelParams p) {
+  using Cfg = TileCfg<BN, CTAS, MODE>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
   constexpr int kUmmaK = INT8 ? 32 : 16;          // K per tcgen05.mma (32 bytes)
@@ -153,6 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int kPanelBytes = kElemsPerRow * kRowBytes;  // K rows x 128 B
   constexpr int kTileM = kBM * CTAS;              // rows of C per tile (per CTA pair when CTAS == 2)
   static_assert(!W_KN || (Cfg::kBRows % kPanelN == 0), "MN-major weight staging needs whole 128-byte panels");
+  static_assert(MODE != kRes || Cfg::kTmaStore, "the residual epilogue needs the TMA-store layout");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -164,7 +290,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t bar_empty = bar_base + 8 * kStages;    // [kStages]
   const uint32_t bar_acc_full = bar_base + 16 * kStages;       // [2]
   const uint32_t bar_acc_empty = bar_base + 16 * kStages + 16; // [2]  (used in the leader CTA only)
-  const uint32_t tmem_slot = bar_base + 16 * kStages + 32;
+  const uint32_t bar_skip = bar_base + 16 * kStages + 32;      // [kEpilogueWarps] skip tile landed (kRes)
+  const uint32_t tmem_slot = bar_skip + 8 * Cfg::kEpilogueWarps;
   __shared__ int abort_flag_storage;
   volatile int* abort_flag = &abort_flag_storage;
 
@@ -190,10 +317,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       ptx::mbar_init(bar_acc_full + 8 * a, 1);
       ptx::mbar_init(bar_acc_empty + 8 * a, Cfg::kEpilogueWarps * CTAS);
     }
+    for (int w = 0; w < Cfg::kEpilogueWarps; ++w) ptx::mbar_init(bar_skip + 8 * w, 1);
     ptx::mbar_init_fence();
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_w);
     if (p.tma_store) ptx::prefetch_tensormap(&map_out);
+    if (MODE == kRes) ptx::prefetch_tensormap(&map_skip);
   }
   if (warp == 1) {
     if (CTAS == 2) {
@@ -295,57 +424,130 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int ew = warp - 2;
     const int quarter = warp & 3;              // TMEM lane quarter this warp may access
     const int half = ew >> 2;                  // which share of the tile's columns (eight-warp layout)
-    constexpr int kColsPerWarp = BN / (Cfg::kEpilogueWarps / 4);
+    constexpr int kColsPerWarp = Cfg::kColsPerWarp;
     const int row_in_tile = quarter * 32 + lane;
-    const uint32_t staging = staging_base + ew * kStagingBytesPerWarp;
+    const uint32_t staging = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
+    const uint32_t skip_bar = bar_skip + 8 * ew;
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;
     uint32_t local = 0;
+    uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
     for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
       const long long m0 = (tile / n_tiles) * kTileM + rank * kBM;
       const int n0 = static_cast<int>(tile % n_tiles) * BN + half * kColsPerWarp;
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
+      const long long row = m0 + row_in_tile;
+      const bool row_ok = row < p.m;
+
+      // ---- everything that can be fetched before the accumulator is complete
+      RowCtx rc;
+      rc.row_ok = row_ok;
+      rc.rs = (INT8 && p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      rc.mean = 0.0f;
+      rc.rstd = 1.0f;
+      if (row_ok) {
+        if (MODE == kLnIn) {
+          row_stats(p.ln_in_stats, p.ln_in_parts, p.m, row, p.ln_in_inv_width, p.ln_eps, rc.mean, rc.rstd);
+        } else if (MODE == kRes) {
+          if (p.res_stats != nullptr) {
+            row_stats(p.res_stats, p.res_parts, p.m, row, p.res_inv_width, p.ln_eps, rc.mean, rc.rstd);
+          }
+        }
+      }
+      if constexpr (MODE == kRes) {
+        // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
+        // buffers, one 32 x 64 box per group.  The buffers are free once the previous tile's stores
+        // have finished reading them.
+        if (lane == 0) {
+          ptx::bulk_wait_read<0>();
+          int boxes = 0;
+#pragma unroll
+          for (int g = 0; g < Cfg::kGroups; ++g) boxes += (n0 + g * 64 < p.n) ? 1 : 0;
+          if (boxes > 0) {
+            ptx::mbar_expect_tx(skip_bar, boxes * kGroupBytes);
+#pragma unroll
+            for (int g = 0; g < Cfg::kGroups; ++g) {
+              if (n0 + g * 64 < p.n) {
+                ptx::tma_load_2d<1>(staging + g * kGroupBytes, &map_skip, n0 + g * 64,
+                                    static_cast<int>(m0) + quarter * 32, skip_bar);
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+
       ok = ptx::mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status, 0x400u + acc);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const long long row = m0 + row_in_tile;
-      const bool row_ok = row < p.m;
-      const float rs = (INT8 && p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      if constexpr (MODE == kRes) {
+        if (n0 < p.n) {
+          ok = ptx::mbar_wait(skip_bar, skip_phase, abort_flag, p.status, 0x500u + ew);
+          if (!ok) break;
+          skip_phase ^= 1u;
+        }
+      }
       const uint32_t taddr_row =
           tmem_base + acc * BN + half * kColsPerWarp + (static_cast<uint32_t>(quarter * 32) << 16);
       if (tma_path) {
         if constexpr (Cfg::kTmaStore) {
 #pragma unroll 1
-          for (int g = 0; g < kColsPerWarp / 64; ++g) {
+          for (int g = 0; g < Cfg::kGroups; ++g) {
             const int col0 = n0 + g * 64;
             if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
-            uint32_t v0[32], v1[32];
-            ptx::tmem_ld_32x32(taddr_row + g * 64, v0);
-            ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, v1);
+            uint32_t v[64];
+            ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            const uint32_t buf = staging + (MODE == kRes ? g : 0) * kGroupBytes;
+            if (MODE != kRes) {
+              // Single staging buffer: it is free once the previous store has finished reading it.
+              if (lane == 0) ptx::bulk_wait_read<0>();
+              __syncwarp();
+            }
             ptx::tc_wait_ld();
-            uint32_t packed[32];
-            finish_chunk_bf16<INT8>(v0, *reinterpret_cast<uint32_t(*)[16]>(&packed[0]), col0, rs, p);
-            finish_chunk_bf16<INT8>(v1, *reinterpret_cast<uint32_t(*)[16]>(&packed[16]), col0 + 32, rs, p);
-            // The staging buffer is free once the previous store has finished reading it.
-            if (lane == 0) ptx::bulk_wait_read<0>();
-            __syncwarp();
-            // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor map expects:
+            const bool whole = p.vec_ok && (col0 + 64 <= p.n);
+            float sum = 0.0f, sumsq = 0.0f;
+            // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor maps use:
             // 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+            const uint32_t row_addr = buf + lane * kRowBytes;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const uint32_t addr = staging + lane * kRowBytes + ((c ^ (lane & 7)) << 4);
-              ptx::st_shared_v4(addr, packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            for (int h = 0; h < 2; ++h) {  // two 32-column halves of the group
+              uint32_t skip_raw[16];
+              if (MODE == kRes) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  uint4 raw;
+                  ptx::ld_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), raw);
+                  skip_raw[4 * c] = raw.x; skip_raw[4 * c + 1] = raw.y;
+                  skip_raw[4 * c + 2] = raw.z; skip_raw[4 * c + 3] = raw.w;
+                }
+              }
+              uint32_t pk[16];
+              if (whole) {
+                finish32<MODE, INT8, true>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
+              } else {
+                finish32<MODE, INT8, false>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
+              }
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
+                                  pk[4 * c + 2], pk[4 * c + 3]);
+              }
+            }
+            if (MODE == kRes) {
+              // One partial per 64 output columns: part index col0 / 64, layout [part][row].
+              if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
             }
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              ptx::tma_store_2d(&map_out, staging, col0, static_cast<int>(m0) + quarter * 32);
+              ptx::tma_store_2d(&map_out, buf, col0, static_cast<int>(m0) + quarter * 32);
               ptx::bulk_commit();
             }
           }
         }
-      } else {
+      } else if constexpr (MODE != kRes) {
 #pragma unroll 1
         for (int c = 0; c < kColsPerWarp / 32; ++c) {
           const int col0 = n0 + c * 32;
@@ -357,7 +559,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const bool full_chunk = (col0 + 32 <= p.n) && p.vec_ok;
           if (p.out_kind == LC0B200_OUT_BF16) {
             uint32_t packed[16];
-            finish_chunk_bf16<INT8>(v, packed, col0, rs, p);
+            float unused_sum = 0.0f, unused_sumsq = 0.0f;
+            finish32<MODE, INT8, false>(v, packed, col0, nullptr, rc, p, unused_sum, unused_sumsq);
             bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
             if (full_chunk) {
 #pragma unroll
@@ -379,7 +582,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < p.n) {
-                float y = acc_value<INT8>(v[j], rs, p.col_scale, col0 + j);
+                float y = acc_value<INT8>(v[j], rc.rs, p.col_scale, col0 + j);
                 if (p.bias != nullptr) y += __bfloat162float(p.bias[col0 + j]);
                 dst[j] = activate_rt(y, p.activation);
               }
@@ -476,9 +679,9 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool INT8, bool W_KN, int CTAS>
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
 int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
-  using Cfg = TileCfg<BN, CTAS>;
+  using Cfg = TileCfg<BN, CTAS, MODE>;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;
   constexpr int kPanelN = INT8 ? 128 : 64;
   const int eb = INT8 ? 1 : 2;
@@ -492,9 +695,14 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
   const bool tma_store = Cfg::kTmaStore && g.out_kind == LC0B200_OUT_BF16 && aligned16(g.out) &&
                          ((g.ldc * out_eb) % 16 == 0);
-  CUtensorMap map_out = map_a;  // placeholder when the direct-store epilogue is used
+  CUtensorMap map_out = map_a, map_skip = map_a;  // placeholders when unused
   if (tma_store && !make_map(&map_out, g.out, 2, g.m, g.n, g.ldc, 32, 64)) return LC0B200_ERR_CUDA;
-  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS>;
+  if (MODE == kRes) {
+    if (!tma_store) return LC0B200_ERR_UNSUPPORTED;
+    if (!aligned16(g.res_skip_bf16) || (g.ld_skip % 8) != 0) return LC0B200_ERR_MISALIGNED;
+    if (!make_map(&map_skip, g.res_skip_bf16, 2, g.m, g.n, g.ld_skip, 32, 64)) return LC0B200_ERR_CUDA;
+  }
+  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -516,8 +724,25 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   p.status = device_status_words();
   if (p.status == nullptr) return LC0B200_ERR_CUDA;
   p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16)) &&
-             (g.col_scale == nullptr || aligned16(g.col_scale));
+             (g.col_scale == nullptr || aligned16(g.col_scale)) &&
+             (g.ln_in_stats == nullptr || (aligned16(g.ln_in_c) && aligned16(g.ln_in_d))) &&
+             (g.res_stats == nullptr || (aligned16(g.res_gamma_bf16) && aligned16(g.res_beta_bf16)));
   p.tma_store = tma_store ? 1 : 0;
+  p.ln_in_stats = reinterpret_cast<const float2*>(g.ln_in_stats);
+  p.ln_in_c = g.ln_in_c;
+  p.ln_in_d = g.ln_in_d;
+  p.ln_in_parts = g.ln_in_parts;
+  p.ln_in_inv_width = 1.0f / static_cast<float>(g.k);
+  p.ln_eps = g.ln_eps;
+  p.res_skip = reinterpret_cast<const bf16*>(g.res_skip_bf16);
+  p.ld_skip = g.ld_skip;
+  p.res_stats = reinterpret_cast<const float2*>(g.res_stats);
+  p.res_gamma = reinterpret_cast<const bf16*>(g.res_gamma_bf16);
+  p.res_beta = reinterpret_cast<const bf16*>(g.res_beta_bf16);
+  p.res_parts = g.res_parts;
+  p.res_inv_width = 1.0f / static_cast<float>(g.n);
+  p.res_alpha = g.res_alpha;
+  p.stats_out = reinterpret_cast<float2*>(g.stats_out);
   const long long tiles = ceil_div_ll(g.m, kBM * CTAS) * ceil_div_ll(g.n, BN);
   const long long max_groups = sm_count() / CTAS;
   const unsigned grid = static_cast<unsigned>((tiles < max_groups ? tiles : max_groups) * CTAS);
@@ -533,7 +758,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = CTAS == 2 ? 1 : 0;
-  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, p) != cudaSuccess) return LC0B200_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, p) != cudaSuccess) return LC0B200_ERR_CUDA;
   return launch_status();
 }
 
@@ -541,25 +766,45 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
 // 256 x 256 tiles to fill 74 pairs and the single-CTA kernel balances better).
 constexpr long long kPairMinRows = 8192;
 
-template <bool INT8, bool W_KN>
+template <bool INT8, bool W_KN, int MODE>
 int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   // MN-major weight staging needs BN to be a whole number of 128-byte panels
   // (64 bf16 or 128 int8 columns); narrower outputs just run a partly empty tile.
   constexpr int kMinBn = W_KN ? (INT8 ? 128 : 64) : 32;
   if (g.n > 128) {
-    if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2>(g, stream);
-    return launch<256, INT8, W_KN, 1>(g, stream);
+    if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
+    return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
   if constexpr (kMinBn <= 128) {
-    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN, 1>(g, stream);
+    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN, 1, MODE>(g, stream);
   }
-  if constexpr (kMinBn <= 64) {
-    if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN, 1>(g, stream);
-  }
-  if constexpr (kMinBn <= 32) {
-    return launch<32, INT8, W_KN, 1>(g, stream);
+  if constexpr (MODE != kRes) {  // narrow tiles have no TMA-store path, which the residual epilogue needs
+    if constexpr (kMinBn <= 64) {
+      if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN, 1, MODE>(g, stream);
+    }
+    if constexpr (kMinBn <= 32) {
+      return launch<32, INT8, W_KN, 1, MODE>(g, stream);
+    }
   }
   return LC0B200_ERR_UNSUPPORTED;
+}
+
+template <bool INT8, bool W_KN>
+int dispatch_mode(const lc0b200_gemm_args& g, cudaStream_t stream) {
+  const bool ln_in = g.ln_in_stats != nullptr;
+  const bool res = g.res_skip_bf16 != nullptr;
+  if (ln_in && res) return LC0B200_ERR_UNSUPPORTED;
+  if ((ln_in || res || g.stats_out != nullptr) && g.out_kind != LC0B200_OUT_BF16) return LC0B200_ERR_UNSUPPORTED;
+  if (g.stats_out != nullptr && !res) return LC0B200_ERR_UNSUPPORTED;
+  if constexpr (INT8) {
+    // The deferred-LayerNorm epilogues are instantiated for bf16 operands only.
+    if (ln_in || res) return LC0B200_ERR_UNSUPPORTED;
+    return dispatch_bn<INT8, W_KN, kPlain>(g, stream);
+  } else {
+    if (ln_in) return dispatch_bn<INT8, W_KN, kLnIn>(g, stream);
+    if (res) return dispatch_bn<INT8, W_KN, kRes>(g, stream);
+    return dispatch_bn<INT8, W_KN, kPlain>(g, stream);
+  }
 }
 
 }  // namespace
@@ -576,8 +821,8 @@ bool gemm_tcgen05_supported(const lc0b200_gemm_args& g) {
 int gemm_tcgen05(const lc0b200_gemm_args& g, cudaStream_t stream) {
   const bool int8 = g.in_type == LC0B200_IN_INT8;
   const bool w_kn = g.w_layout == LC0B200_W_KN;
-  if (int8) return w_kn ? dispatch_bn<true, true>(g, stream) : dispatch_bn<true, false>(g, stream);
-  return w_kn ? dispatch_bn<false, true>(g, stream) : dispatch_bn<false, false>(g, stream);
+  if (int8) return w_kn ? dispatch_mode<true, true>(g, stream) : dispatch_mode<true, false>(g, stream);
+  return w_kn ? dispatch_mode<false, true>(g, stream) : dispatch_mode<false, false>(g, stream);
 }
 
 }  // namespace lc0b200

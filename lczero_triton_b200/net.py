@@ -41,6 +41,8 @@ class _Dense:
     k: int
     bias: torch.Tensor | None = None
     col_scale: torch.Tensor | None = None  # f32 [n] for int8 weights
+    fold_c: torch.Tensor | None = None  # f32 [n]: column sums of the gamma-scaled weight (deferred LayerNorm)
+    fold_d: torch.Tensor | None = None  # f32 [n]: beta^T W + bias
 
 
 def quantize_weight_per_channel(w_kn: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -57,7 +59,7 @@ class Bt4Net:
     """A BT4-style network resident on one GPU."""
 
     def __init__(self, weights: Mapping[str, torch.Tensor], config: NetConfig, *, device: str | torch.device = "cuda",
-                 mode: str = "bf16", weight_layout: str = "nk") -> None:
+                 mode: str = "bf16", weight_layout: str = "nk", deferred_layer_norm: bool | None = None) -> None:
         if mode not in ("bf16", "int8"):
             raise ValueError("mode must be 'bf16' or 'int8'")
         if weight_layout not in ("nk", "kn"):
@@ -70,6 +72,11 @@ class Bt4Net:
             raise ValueError("Bt4Net needs a CUDA device; there is no CPU path")
         if self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
+        # bf16 mode keeps the residual stream un-normalised between GEMMs ("deferred LayerNorm"): the
+        # two LayerNorm launches per encoder layer become epilogue arithmetic (see lc0b200_gemm_args).
+        self.deferred = (mode == "bf16") if deferred_layer_norm is None else bool(deferred_layer_norm)
+        if self.deferred and mode != "bf16":
+            raise ValueError("deferred LayerNorm is implemented for the bf16 mode only")
         self._layout = _lib.W_NK if weight_layout == "nk" else _lib.W_KN
         self._w = {k: v.to(device=self.device, dtype=torch.bfloat16).contiguous() for k, v in weights.items()}
         self._scalars = {k: float(v.float().reshape(-1)[0]) for k, v in weights.items() if v.numel() == 1}
@@ -105,6 +112,23 @@ class Bt4Net:
             return _Dense(packed, _lib.W_NK, n, k, bias)
         return _Dense(w_kn, _lib.W_KN, n, k, bias)
 
+    def _dense_folded(self, names: list[str], biases: list[str] | None, gamma: str, beta: str) -> _Dense:
+        """Dense layer(s) consuming a deferred-LayerNorm input: the weight is pre-scaled by the
+        LayerNorm's gamma and two per-column vectors carry the mean and beta terms."""
+        w = torch.cat([self._w[n] for n in names], dim=1).float()  # [K, N], bf16 values
+        g, b = self._w[gamma].float(), self._w[beta].float()
+        scaled = (w * g[:, None]).to(torch.bfloat16)
+        fold_c = scaled.float().sum(dim=0).contiguous()
+        fold_d = b @ w
+        if biases is not None:
+            fold_d = fold_d + torch.cat([self._w[x] for x in biases]).float()
+        k, n = scaled.shape
+        if self._layout == _lib.W_NK:
+            packed = torch.empty((n, k), dtype=torch.bfloat16, device=self.device)
+            ops.transpose(packed, scaled.contiguous(), k, n)
+            return _Dense(packed, _lib.W_NK, n, k, None, None, fold_c, fold_d.contiguous())
+        return _Dense(scaled.contiguous(), _lib.W_KN, n, k, None, None, fold_c, fold_d.contiguous())
+
     def _prepare(self) -> None:
         q8 = self.mode == "int8"
         d = self._dense
@@ -126,6 +150,20 @@ class Bt4Net:
                 "ffn1": d(f"{p}/ffn/dense1/w/w", f"{p}/ffn/dense1/b/w", int8=q8),
                 "ffn2": d(f"{p}/ffn/dense2/w/w", int8=q8),
             })
+        if self.deferred:
+            self.zero_bias = torch.zeros(self.cfg.embedding, dtype=torch.bfloat16, device=self.device)
+            for i, layer in enumerate(self.layers):
+                p = f"/encoder{i}"
+                prev = "/attn_body/ln2" if i == 0 else f"/encoder{i - 1}/ln2"
+                layer["qkv_f"] = self._dense_folded([f"{p}/mha/Q/w/w", f"{p}/mha/K/w/w", f"{p}/mha/V/w/w"],
+                                                    [f"{p}/mha/Q/b/w", f"{p}/mha/K/b/w", f"{p}/mha/V/b/w"],
+                                                    f"{prev}/w/scale", f"{prev}/w/bias")
+                layer["compress_f"] = self._dense_folded([f"{p}/smolgen/compress/w"], None,
+                                                         f"{prev}/w/scale", f"{prev}/w/bias")
+                layer["ffn1_f"] = self._dense_folded([f"{p}/ffn/dense1/w/w"], [f"{p}/ffn/dense1/b/w"],
+                                                     f"{p}/ln1/w/scale", f"{p}/ln1/w/bias")
+                layer["out_b"] = self._w[f"{p}/mha/out/dense/b/w"]
+                layer["ffn2_b"] = self._w[f"{p}/ffn/dense2/b/w"]
         self.pol1 = d("/policy/dense1/matmul/w", "/policy/dense1/add/w")
         self.pol_q = d("/policy/Q/matmul/w", "/policy/Q/add/w")
         self.pol_k = d("/policy/K/matmul/w", "/policy/K/add/w")
@@ -169,6 +207,11 @@ class Bt4Net:
             "wdl": torch.empty((b, 3), dtype=torch.float32, device=dev),
             "mlh": torch.empty((b, 1), dtype=torch.float32, device=dev),
         }
+        if self.deferred:
+            parts = (c.embedding + 63) // 64
+            for name in ("stats0", "stats1", "stats2"):
+                ws[name] = torch.empty((parts, t, 2), dtype=torch.float32, device=dev)
+            ws["ln_tap"] = bf(t, c.embedding)
         if self.mode == "int8":
             ws["q_d"] = torch.empty((t, c.embedding), dtype=torch.int8, device=dev)
             ws["q_f"] = torch.empty((t, c.ffn), dtype=torch.int8, device=dev)
@@ -191,48 +234,37 @@ class Bt4Net:
                               activation=activation, epsilon=self.cfg.ln_eps, skip=skip,
                               alpha=None if alpha is None else self._w[alpha], q_out=q_out, q_scale=q_scale)
 
-    # ------------------------------------------------------------------ forward
-    @torch.no_grad()
-    def forward(self, plane_masks: torch.Tensor, plane_values: torch.Tensor,
-                taps: dict[str, torch.Tensor] | None = None):
-        """Run the network on device-resident packed planes.  The returned tensors are
-        workspace buffers that the next call with the same batch size overwrites."""
-        if plane_masks.dtype != torch.int64 or plane_values.dtype != torch.float32:
-            raise ValueError("plane_masks must be int64 (u64 bit patterns) and plane_values float32")
-        if plane_masks.shape != plane_values.shape or plane_masks.dim() != 2 or plane_masks.shape[1] != INPUT_PLANES:
-            raise ValueError("inputs must both have shape [B, 112]")
-        if plane_masks.device != self.device or plane_values.device != self.device:
-            raise ValueError(f"inputs must live on {self.device}")
-        plane_masks, plane_values = plane_masks.contiguous(), plane_values.contiguous()
+    # ------------------------------------------------------------------ encoder tower
+    def _smolgen_and_attention(self, ws, layer, i: int, b: int) -> None:
+        """Per-position 64x64 logit bias for every head (network.py:778-849, 943-955), then the fused
+        attention (network.py:1004-1047).  Expects ``ws["compressed"]`` and ``ws["qkv"]``."""
         c = self.cfg
-        b = plane_masks.shape[0]
-        t = b * SQUARES
+        p = f"/encoder{i}"
         d, h = c.embedding, c.heads
-        ws = self._workspace(b)
+        self._gemm(ws["sg_hidden"], ws["compressed"], layer["sg1"], b)
+        self._ln(ws["sg_hidden"], ws["sg_hidden"], f"{p}/smolgen/dense1/b/w", f"{p}/smolgen/ln1/w/scale",
+                 f"{p}/smolgen/ln1/w/bias", b, c.smolgen_hidden, activation="swish")
+        self._gemm(ws["sg_gen"], ws["sg_hidden"], layer["sg2"], b)
+        self._ln(ws["sg_gen"], ws["sg_gen"], f"{p}/smolgen/dense2/b/w", f"{p}/smolgen/ln2/w/scale",
+                 f"{p}/smolgen/ln2/w/bias", b, h * c.smolgen_gen, activation="swish")
+        self._gemm(ws["sg_bias"], ws["sg_gen"], self.smolgen_shared, b * h)
+        qkv = ws["qkv"]
+        ops.attention(ws["merged"], qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:], ws["sg_bias"],
+                      self._scalars[f"{p}/mha/QK/scale/w"], b, h, c.head_depth, ldq=3 * d, ldk=3 * d, ldv=3 * d, ldo=d)
+
+    def _tower(self, ws, skip: torch.Tensor, b: int, tap) -> torch.Tensor:
+        """Embedding FFN tail and the encoder layers with stand-alone LayerNorm launches."""
+        c = self.cfg
+        t = b * SQUARES
+        d = c.embedding
         q8 = self.mode == "int8"
         qd, qf, qs = (ws["q_d"], ws["q_f"], ws["q_scale"]) if q8 else (None, None, None)
-
-        def tap(name: str, x: torch.Tensor) -> None:
-            if taps is not None:
-                taps[name] = x.detach().clone()
-
-        # ---- input embedding (network.py:458-642)
-        ops.embed_position_input(ws["pos_in"], plane_masks, plane_values, b)
-        self._gemm(ws["position"], ws["pos_in"], self.pe, b)
-        ops.embed_concat(ws["emb_in"], plane_masks, plane_values, ws["position"], b, c.pos_enc)
-        self._gemm(ws["branch"], ws["emb_in"], self.emb, t)
-        skip = self._ln(ws["x0"], ws["branch"], "/attn_body/add/w", "/attn_body/ln/w/scale", "/attn_body/ln/w/bias",
-                        t, d, activation="mish")
-        ops.input_gating(skip, skip, self._w["/ip_mul_gate/w"], self._w["/ip_add_gate/w"], b, SQUARES, d)
-        self._gemm(ws["hidden"], skip, self.emb_ffn1, t, activation="mish")
         self._gemm(ws["branch"], ws["hidden"], self.emb_ffn2, t)
         body = self._ln(ws["x1"], ws["branch"], "/attn_body/ffn/dense2/b/w", "/attn_body/ln2/w/scale",
                         "/attn_body/ln2/w/bias", t, d, skip=skip, alpha="/attn_body/ffn/alpha/w",
                         q_out=qd, q_scale=qs)
         tap("embedding", body)
         free = [ws["x0"], ws["x2"]]  # residual-stream buffers not holding `body`
-
-        # ---- encoder tower (network.py:653-669)
         for i, layer in enumerate(self.layers):
             p = f"/encoder{i}"
             # QKV first in int8 mode: it consumes the quantised copy of `body` before anything overwrites it.
@@ -240,20 +272,8 @@ class Bt4Net:
                 self._gemm(ws["qkv"], qd, layer["qkv"], t, row_scale=qs)
             else:
                 self._gemm(ws["qkv"], body, layer["qkv"], t)
-            # smolgen: per-position 64x64 logit bias for every head (network.py:778-849, 943-955)
             self._gemm(ws["compressed"], body, layer["compress"], t)
-            self._gemm(ws["sg_hidden"], ws["compressed"], layer["sg1"], b)
-            self._ln(ws["sg_hidden"], ws["sg_hidden"], f"{p}/smolgen/dense1/b/w", f"{p}/smolgen/ln1/w/scale",
-                     f"{p}/smolgen/ln1/w/bias", b, c.smolgen_hidden, activation="swish")
-            self._gemm(ws["sg_gen"], ws["sg_hidden"], layer["sg2"], b)
-            self._ln(ws["sg_gen"], ws["sg_gen"], f"{p}/smolgen/dense2/b/w", f"{p}/smolgen/ln2/w/scale",
-                     f"{p}/smolgen/ln2/w/bias", b, h * c.smolgen_gen, activation="swish")
-            self._gemm(ws["sg_bias"], ws["sg_gen"], self.smolgen_shared, b * h)
-            # fused attention (network.py:1004-1047)
-            qkv = ws["qkv"]
-            ops.attention(ws["merged"], qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:], ws["sg_bias"],
-                          self._scalars[f"{p}/mha/QK/scale/w"], b, h, c.head_depth,
-                          ldq=3 * d, ldk=3 * d, ldv=3 * d, ldo=d)
+            self._smolgen_and_attention(ws, layer, i, b)
             if q8:
                 ops.quantize_rows(qd, qs, ws["merged"], t, d)
                 self._gemm(ws["branch"], qd, layer["out"], t, row_scale=qs)
@@ -275,6 +295,94 @@ class Bt4Net:
             free = [body, attended]
             body = new_body
             tap(f"encoder{i}", body)
+        return body
+
+    def _gemm_folded(self, out: torch.Tensor, a: torch.Tensor, layer: _Dense, m: int, stats: torch.Tensor, *,
+                     activation: str = "none") -> torch.Tensor:
+        return ops.gemm(out, a, layer.w, m=m, n=layer.n, k=layer.k, activation=activation, w_layout=layer.layout,
+                        ln_in=(stats, layer.fold_c, layer.fold_d), ln_eps=self.cfg.ln_eps)
+
+    def _tower_deferred(self, ws, skip: torch.Tensor, b: int, tap) -> torch.Tensor:
+        """The same layers with the residual stream kept un-normalised: every residual GEMM stores
+        z = alpha * (branch + bias) + LN(previous z) with per-row partial sums, and every GEMM that
+        reads the stream applies the pending LayerNorm in its epilogue.  No LayerNorm kernel runs
+        inside the tower; one materialises the final body for the heads."""
+        c = self.cfg
+        t = b * SQUARES
+        d = c.embedding
+        eps = c.ln_eps
+        w = self._w
+
+        def materialise(z: torch.Tensor, ln: str, out: torch.Tensor) -> torch.Tensor:
+            return ops.layer_norm(out, z, self.zero_bias, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], row_count=t, width=d,
+                                  epsilon=eps)
+
+        # embedding FFN tail: z = alpha * (hidden @ W2 + b2) + skip   (skip is a plain tensor here)
+        z, stats, ln = ws["x1"], ws["stats0"], "/attn_body/ln2"
+        ops.gemm(z, ws["hidden"], self.emb_ffn2.w, m=t, n=d, k=self.emb_ffn2.k, bias=w["/attn_body/ffn/dense2/b/w"],
+                 w_layout=self.emb_ffn2.layout, res_skip=skip, res_alpha=self._scalars["/attn_body/ffn/alpha/w"],
+                 stats_out=stats, ln_eps=eps)
+        if tap is not None:
+            tap("embedding", materialise(z, ln, ws["ln_tap"]))
+        free_z = [ws["x0"], ws["x2"]]
+        free_s = [ws["stats1"], ws["stats2"]]
+        for i, layer in enumerate(self.layers):
+            p = f"/encoder{i}"
+            self._gemm_folded(ws["qkv"], z, layer["qkv_f"], t, stats)
+            self._gemm_folded(ws["compressed"], z, layer["compress_f"], t, stats)
+            self._smolgen_and_attention(ws, layer, i, b)
+            z1, stats1 = free_z[0], free_s[0]
+            ops.gemm(z1, ws["merged"], layer["out"].w, m=t, n=d, k=d, bias=layer["out_b"], w_layout=layer["out"].layout,
+                     res_skip=z, res_ln=(stats, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"]),
+                     res_alpha=self._scalars[f"{p}/alpha*input/w"], stats_out=stats1, ln_eps=eps)
+            self._gemm_folded(ws["hidden"], z1, layer["ffn1_f"], t, stats1, activation="mish")
+            z2, stats2 = free_z[1], free_s[1]
+            ops.gemm(z2, ws["hidden"], layer["ffn2"].w, m=t, n=d, k=c.ffn, bias=layer["ffn2_b"],
+                     w_layout=layer["ffn2"].layout, res_skip=z1,
+                     res_ln=(stats1, w[f"{p}/ln1/w/scale"], w[f"{p}/ln1/w/bias"]),
+                     res_alpha=self._scalars[f"{p}/ffn/alpha/w"], stats_out=stats2, ln_eps=eps)
+            free_z, free_s = [z, z1], [stats, stats1]
+            z, stats, ln = z2, stats2, f"{p}/ln2"
+            if tap is not None:
+                tap(f"encoder{i}", materialise(z, ln, ws["ln_tap"]))
+        return materialise(z, ln, free_z[0])
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward(self, plane_masks: torch.Tensor, plane_values: torch.Tensor,
+                taps: dict[str, torch.Tensor] | None = None):
+        """Run the network on device-resident packed planes.  The returned tensors are
+        workspace buffers that the next call with the same batch size overwrites."""
+        if plane_masks.dtype != torch.int64 or plane_values.dtype != torch.float32:
+            raise ValueError("plane_masks must be int64 (u64 bit patterns) and plane_values float32")
+        if plane_masks.shape != plane_values.shape or plane_masks.dim() != 2 or plane_masks.shape[1] != INPUT_PLANES:
+            raise ValueError("inputs must both have shape [B, 112]")
+        if plane_masks.device != self.device or plane_values.device != self.device:
+            raise ValueError(f"inputs must live on {self.device}")
+        plane_masks, plane_values = plane_masks.contiguous(), plane_values.contiguous()
+        c = self.cfg
+        b = plane_masks.shape[0]
+        t = b * SQUARES
+        d, h = c.embedding, c.heads
+        ws = self._workspace(b)
+
+        def tap(name: str, x: torch.Tensor) -> None:
+            if taps is not None:
+                taps[name] = x.detach().clone()
+
+        # ---- input embedding (network.py:458-642)
+        ops.embed_position_input(ws["pos_in"], plane_masks, plane_values, b)
+        self._gemm(ws["position"], ws["pos_in"], self.pe, b)
+        ops.embed_concat(ws["emb_in"], plane_masks, plane_values, ws["position"], b, c.pos_enc)
+        self._gemm(ws["branch"], ws["emb_in"], self.emb, t)
+        skip = self._ln(ws["x0"], ws["branch"], "/attn_body/add/w", "/attn_body/ln/w/scale", "/attn_body/ln/w/bias",
+                        t, d, activation="mish")
+        ops.input_gating(skip, skip, self._w["/ip_mul_gate/w"], self._w["/ip_add_gate/w"], b, SQUARES, d)
+        self._gemm(ws["hidden"], skip, self.emb_ffn1, t, activation="mish")
+        if self.deferred:
+            body = self._tower_deferred(ws, skip, b, tap if taps is not None else None)
+        else:
+            body = self._tower(ws, skip, b, tap)
 
         # ---- policy head (network.py:1261-1356)
         self._gemm(ws["pol_emb"], body, self.pol1, t, activation="mish")

@@ -120,8 +120,17 @@ _OUT_KIND = {torch.bfloat16: _lib.OUT_BF16, torch.float32: _lib.OUT_F32, torch.i
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, *, m: int, n: int, k: int,
          bias: torch.Tensor | None = None, activation: str = "none", w_layout: int = _lib.W_NK,
          row_scale: torch.Tensor | None = None, col_scale: torch.Tensor | None = None,
-         lda: int | None = None, ldw: int | None = None, ldc: int | None = None, simt: bool = False) -> torch.Tensor:
-    """Tensor-core GEMM with fused epilogue (``include/lc0b200.h``: lc0b200_gemm)."""
+         lda: int | None = None, ldw: int | None = None, ldc: int | None = None, simt: bool = False,
+         ln_in: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None, ln_eps: float = 1e-3,
+         res_skip: torch.Tensor | None = None, res_alpha: float = 1.0,
+         res_ln: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+         stats_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core GEMM with fused epilogue (``include/lc0b200.h``: lc0b200_gemm).
+
+    Deferred LayerNorm: ``ln_in=(stats [parts,m,2] f32, c [n] f32, d [n] f32)`` folds the LayerNorm of
+    the rows of ``a`` into the epilogue; ``res_skip`` (+ ``res_ln=(stats, gamma, beta)`` when the skip
+    operand is itself deferred) adds ``res_alpha * y`` to it; ``stats_out [ceil(n/64), m, 2]`` receives
+    the partial sums of the stored rows."""
     if a.dtype not in (torch.bfloat16, torch.int8) or w.dtype != a.dtype:
         raise ValueError("a and w must both be bfloat16 or both int8")
     args = GemmArgs()
@@ -135,6 +144,17 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, *, m: int, n: int,
     args.out_kind = _OUT_KIND[out.dtype]
     args.w_layout = w_layout
     args.activation = ACTIVATIONS[activation]
+    args.ln_eps = ln_eps
+    if ln_in is not None:
+        stats, c, d = ln_in
+        args.ln_in_stats, args.ln_in_c, args.ln_in_d, args.ln_in_parts = _p(stats), _p(c), _p(d), stats.shape[0]
+    if res_skip is not None:
+        args.res_skip_bf16, args.ld_skip, args.res_alpha = _p(res_skip), res_skip.stride(0), res_alpha
+        if res_ln is not None:
+            stats, gamma, beta = res_ln
+            args.res_stats, args.res_gamma_bf16, args.res_beta_bf16 = _p(stats), _p(gamma), _p(beta)
+            args.res_parts = stats.shape[0]
+    args.stats_out = _p(stats_out)
     fn = _lib.load().lc0b200_gemm_simt if simt else _lib.load().lc0b200_gemm
     check(fn(ctypes.byref(args), _stream()), "gemm")
     return out

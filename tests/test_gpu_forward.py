@@ -36,10 +36,11 @@ def _relative_to_spread(got: torch.Tensor, want: torch.Tensor) -> float:
     return float((got - want).abs().max() / want.std().clamp_min(1e-12))
 
 
-def _run(pkg, cfg, batch: int, *, mode: str = "bf16", layout: str = "nk", seed: int = 0, std: float = 0.02):
+def _run(pkg, cfg, batch: int, *, mode: str = "bf16", layout: str = "nk", seed: int = 0, std: float = 0.02,
+         deferred: bool | None = None):
     weights = pkg["weights"].random_weights(cfg, seed, std=std)
     masks, values = pkg["synthetic"].synthetic_planes(batch, seed)
-    net = pkg["net"].Bt4Net(weights, cfg, mode=mode, weight_layout=layout)
+    net = pkg["net"].Bt4Net(weights, cfg, mode=mode, weight_layout=layout, deferred_layer_norm=deferred)
     taps: dict[str, torch.Tensor] = {}
     policy, wdl, mlh = net.forward(masks.cuda(), values.cuda(), taps=taps)
     torch.cuda.synchronize()
@@ -50,11 +51,12 @@ def _run(pkg, cfg, batch: int, *, mode: str = "bf16", layout: str = "nk", seed: 
     return weights, masks, values, (policy.cpu(), wdl.cpu(), mlh.cpu()), {k: v.float().cpu() for k, v in taps.items()}
 
 
+@pytest.mark.parametrize("deferred", [True, False], ids=["deferred-ln", "standalone-ln"])
 @pytest.mark.parametrize("layout", ["nk", "kn"])
 @pytest.mark.parametrize("batch", [1, 3, 32])
-def test_tiny_network_matches_fp32_oracle(pkg, batch, layout) -> None:
+def test_tiny_network_matches_fp32_oracle(pkg, batch, layout, deferred) -> None:
     cfg = pkg["config"].TINY
-    weights, masks, values, got, taps = _run(pkg, cfg, batch, layout=layout)
+    weights, masks, values, got, taps = _run(pkg, cfg, batch, layout=layout, deferred=deferred)
     want_taps: dict[str, torch.Tensor] = {}
     want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps)
     for name in ("embedding", *[f"encoder{i}" for i in range(cfg.layers)]):
@@ -65,10 +67,11 @@ def test_tiny_network_matches_fp32_oracle(pkg, batch, layout) -> None:
     assert _relative_to_spread(got[1], want[1]) < 0.15
 
 
+@pytest.mark.parametrize("deferred", [True, False], ids=["deferred-ln", "standalone-ln"])
 @pytest.mark.parametrize("name", ["BT3", "BT4"])
-def test_full_shape_networks_match_fp32_oracle(pkg, name) -> None:
+def test_full_shape_networks_match_fp32_oracle(pkg, name, deferred) -> None:
     cfg = getattr(pkg["config"], name)
-    weights, masks, values, got, taps = _run(pkg, cfg, 4)
+    weights, masks, values, got, taps = _run(pkg, cfg, 4, deferred=deferred)
     want_taps: dict[str, torch.Tensor] = {}
     want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps)
     for stage in ("embedding", "encoder0", f"encoder{cfg.layers - 1}"):

@@ -170,6 +170,60 @@ def test_linear_int8_equals_quantise_then_gemm(ops, m, n, k) -> None:
     assert torch.equal(scratch_q.cpu(), want_q) and torch.equal(scratch_s.cpu(), want_s)
 
 
+def _partial_stats(z: torch.Tensor) -> torch.Tensor:
+    """[parts, m, 2] partial (sum, sum of squares) over 64-column groups, as the GEMM epilogue emits them."""
+    m, n = z.shape
+    groups = z.float().reshape(m, n // 64, 64)
+    return torch.stack((groups.sum(dim=2), (groups * groups).sum(dim=2)), dim=2).permute(1, 0, 2).contiguous()
+
+
+@pytest.mark.parametrize("m", [1000, 9000])
+def test_deferred_layer_norm_epilogues(ops, m) -> None:
+    """Producer: z = alpha * (A W + b) + LN(z_prev) with partial row sums.  Consumer: LN(z) W' folded into
+    the epilogue.  Both against the oracle's explicit LayerNorm (layer_norm.py:57-87 semantics)."""
+    from lczero_triton_b200 import _lib
+
+    d, f, eps, alpha = 1024, 1536, 1e-3, 0.4273
+    g = _gen(170)
+    z_prev = (torch.randn((m, d), generator=g) * 1.3 + 0.2).to(BF16)
+    gamma, beta = (1 + 0.1 * torch.randn(d, generator=g)).to(BF16), (0.1 * torch.randn(d, generator=g)).to(BF16)
+    a = (torch.randn((m, f), generator=g) * 0.5).to(BF16)
+    w = (torch.randn((f, d), generator=g) * 0.05).to(BF16)
+    bias = (torch.randn(d, generator=g) * 0.1).to(BF16)
+    zero = torch.zeros(d)
+    skip_ln = O.layer_norm(z_prev, zero, gamma, beta, "none", eps)
+    want_z = alpha * (O.matmul(a, w) + bias.float()) + skip_ln
+    stats_prev = _partial_stats(z_prev).cuda()
+    z = torch.empty((m, d), dtype=BF16, device="cuda")
+    stats = torch.full((d // 64, m, 2), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemm(z, a.cuda(), w.t().contiguous().cuda(), m=m, n=d, k=f, bias=bias.cuda(), w_layout=_lib.W_NK,
+             res_skip=z_prev.cuda(), res_ln=(stats_prev, gamma.cuda(), beta.cuda()), res_alpha=alpha,
+             stats_out=stats, ln_eps=eps)
+    torch.testing.assert_close(z.float().cpu(), want_z, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(stats.cpu(), _partial_stats(z.cpu()), rtol=1e-4, atol=1e-3)
+
+    # plain skip operand (the embedding's residual)
+    z_plain = torch.empty((m, d), dtype=BF16, device="cuda")
+    stats_plain = torch.empty_like(stats)
+    ops.gemm(z_plain, a.cuda(), w.t().contiguous().cuda(), m=m, n=d, k=f, bias=bias.cuda(), w_layout=_lib.W_NK,
+             res_skip=z_prev.cuda(), res_alpha=alpha, stats_out=stats_plain, ln_eps=eps)
+    torch.testing.assert_close(z_plain.float().cpu(), alpha * (O.matmul(a, w) + bias.float()) + z_prev.float(),
+                               rtol=1e-2, atol=2e-2)
+
+    # consumer: mish(LN(z) W1 + b1) with gamma folded into the weight
+    zc = z.cpu()
+    w1 = (torch.randn((d, f), generator=g) * 0.03).to(BF16)
+    b1 = (torch.randn(f, generator=g) * 0.1).to(BF16)
+    scaled = (w1.float() * gamma.float()[:, None]).to(BF16)
+    fold_c = scaled.float().sum(dim=0)
+    fold_d = beta.float() @ w1.float() + b1.float()
+    want_h = O.activate(O.matmul(O.layer_norm(zc, zero, gamma, beta, "none", eps), w1) + b1.float(), "mish")
+    hidden = torch.empty((m, f), dtype=BF16, device="cuda")
+    ops.gemm(hidden, z, scaled.t().contiguous().cuda(), m=m, n=f, k=d, activation="mish", w_layout=_lib.W_NK,
+             ln_in=(stats, fold_c.cuda(), fold_d.cuda()), ln_eps=eps)
+    torch.testing.assert_close(hidden.float().cpu(), want_h, rtol=2e-2, atol=2e-2)
+
+
 def test_gemm_linearity_at_full_size(ops) -> None:
     """Size-independent property at the benchmark's row count: GEMM(a1 + a2) = GEMM(a1) + GEMM(a2)
     when the sums are exact in bf16 (small integers), checked on sampled rows of a 262144-row problem."""
