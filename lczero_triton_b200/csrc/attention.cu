@@ -60,8 +60,17 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// clamp(v, -131008, 131008) that keeps NaN (min.NaN / max.NaN return NaN if an input is NaN).
 __device__ __forceinline__ float clamp_keep_nan(float v) {
-  return (v != v) ? v : fminf(fmaxf(v, -kClamp), kClamp);
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(v), "f"(-kClamp));
+  asm("min.NaN.f32 %0, %0, %1;" : "+f"(r) : "f"(kClamp));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 
 struct AttnParams {
@@ -80,14 +89,16 @@ __device__ __forceinline__ void load_head(uint8_t* stage, const AttnParams& p, l
   const long long b = item / p.heads;
   const int h = static_cast<int>(item % p.heads);
   const uint32_t s = smem_addr(stage);
-  const bf16* base[3] = {p.q, p.k, p.v};
-  const long long ld[3] = {p.ldq, p.ldk, p.ldv};
+  // 3 tiles x 64 rows x 4 chunks of 16 bytes: thread t moves chunks t and t + 128 of each tile.
 #pragma unroll
-  for (int it = 0; it < 6; ++it) {  // 3 tiles x 64 rows x 4 chunks = 768 chunks over 128 threads
-    const int c = threadIdx.x + it * 128;
-    const int which = c >> 8, rc = c & 255, row = rc >> 2, ch = rc & 3;
-    const bf16* src = base[which] + (b * 64 + row) * ld[which] + h * 32 + ch * 8;
-    cp_async16(s + which * kTileBytes + row * kRowStride + ch * 16, src);
+  for (int it = 0; it < 2; ++it) {
+    const int rc = threadIdx.x + it * 128, row = rc >> 2, ch = rc & 3;
+    const long long tok = b * 64 + row;
+    const uint32_t dst = s + row * kRowStride + ch * 16;
+    const int col = h * 32 + ch * 8;
+    cp_async16(dst, p.q + tok * p.ldq + col);
+    cp_async16(dst + kTileBytes, p.k + tok * p.ldk + col);
+    cp_async16(dst + 2 * kTileBytes, p.v + tok * p.ldv + col);
   }
   if (p.bias != nullptr) {
     const bf16* src = p.bias + item * 4096;
@@ -157,13 +168,18 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+    // exp(v - max) as exp2(v * log2e - max * log2e): one fused multiply-add and one ex2 per score.
+    // P stays un-normalised (values in (0, 1]) for the second product; the 16 x 32 result is scaled
+    // by 1 / sum afterwards, which costs half as many multiplies as scaling P.
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float off0 = mx0 * kLog2e, off1 = mx1 * kLog2e;
     float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      s[j][0] = __expf(s[j][0] - mx0);
-      s[j][1] = __expf(s[j][1] - mx0);
-      s[j][2] = __expf(s[j][2] - mx1);
-      s[j][3] = __expf(s[j][3] - mx1);
+      s[j][0] = fast_exp2(fmaf(s[j][0], kLog2e, -off0));
+      s[j][1] = fast_exp2(fmaf(s[j][1], kLog2e, -off0));
+      s[j][2] = fast_exp2(fmaf(s[j][2], kLog2e, -off1));
+      s[j][3] = fast_exp2(fmaf(s[j][3], kLog2e, -off1));
       sum0 += s[j][0] + s[j][1];
       sum1 += s[j][2] + s[j][3];
     }
@@ -180,10 +196,10 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
 #pragma unroll
     for (int step = 0; step < 4; ++step) {  // 16 keys per step
       uint32_t pa[4];
-      pa[0] = pack_bf16x2(s[2 * step][0] * inv0, s[2 * step][1] * inv0);
-      pa[1] = pack_bf16x2(s[2 * step][2] * inv1, s[2 * step][3] * inv1);
-      pa[2] = pack_bf16x2(s[2 * step + 1][0] * inv0, s[2 * step + 1][1] * inv0);
-      pa[3] = pack_bf16x2(s[2 * step + 1][2] * inv1, s[2 * step + 1][3] * inv1);
+      pa[0] = pack_bf16x2(s[2 * step][0], s[2 * step][1]);
+      pa[1] = pack_bf16x2(s[2 * step][2], s[2 * step][3]);
+      pa[2] = pack_bf16x2(s[2 * step + 1][0], s[2 * step + 1][1]);
+      pa[3] = pack_bf16x2(s[2 * step + 1][2], s[2 * step + 1][3]);
 #pragma unroll
       for (int jj = 0; jj < 4; jj += 2) {
         uint32_t vb[4];
@@ -191,6 +207,13 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
         mma_16816(o[jj], pa, vb[0], vb[1]);
         mma_16816(o[jj + 1], pa, vb[2], vb[3]);
       }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[j][0] *= inv0;
+      o[j][1] *= inv0;
+      o[j][2] *= inv1;
+      o[j][3] *= inv1;
     }
     // ---- stage O through this warp's own (now dead) Q rows, then 16-byte coalesced stores
     __syncwarp();

