@@ -456,12 +456,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      if (tma_path) {
+        // The staging buffers are free once the previous tile's stores have finished reading them;
+        // those were issued a whole main loop ago, so this wait is normally already satisfied.
+        if (lane == 0) ptx::bulk_wait_read<0>();
+        __syncwarp();
+      }
       if constexpr (MODE == kRes) {
         // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
-        // buffers, one 32 x 64 box per group.  The buffers are free once the previous tile's stores
-        // have finished reading them.
+        // buffers, one 32 x 64 box per group.
         if (lane == 0) {
-          ptx::bulk_wait_read<0>();
           int boxes = 0;
 #pragma unroll
           for (int g = 0; g < Cfg::kGroups; ++g) boxes += (n0 + g * 64 < p.n) ? 1 : 0;
@@ -491,6 +495,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       const uint32_t taddr_row =
           tmem_base + acc * BN + half * kColsPerWarp + (static_cast<uint32_t>(quarter * 32) << 16);
+      bool released = false;  // accumulator already handed back to the MMA issuer
       if (tma_path) {
         if constexpr (Cfg::kTmaStore) {
 #pragma unroll 1
@@ -501,12 +506,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             const uint32_t buf = staging + g * kGroupBytes;
-            if (MODE != kRes) {
-              // Buffer g was last read by the store issued kGroups stores ago: allow the younger ones
-              // to be still in flight.
-              if (lane == 0) ptx::bulk_wait_read<Cfg::kGroups - 1>();
-              __syncwarp();
-            }
             ptx::tc_wait_ld();
             const bool whole = p.vec_ok && (col0 + 64 <= p.n);
             float sum = 0.0f, sumsq = 0.0f;
@@ -541,10 +540,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               // One partial per 64 output columns: part index col0 / 64, layout [part][row].
               if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
             }
+          }
+          // TMEM has been read out: hand the accumulator back before the stores are even issued.
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if (CTAS == 2) {
+              ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_acc_empty + 8 * acc, 0u));  // the leader's barrier
+            } else {
+              ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+            }
+          }
+          released = true;
+          // One proxy fence per tile and warp (it is by far the most expensive instruction here),
+          // then the stores of all groups.
+          if (n0 < p.n) {
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              ptx::tma_store_2d(&map_out, buf, col0, static_cast<int>(m0) + quarter * 32);
+#pragma unroll
+              for (int g = 0; g < Cfg::kGroups; ++g) {
+                if (n0 + g * 64 < p.n) {
+                  ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
+                                    static_cast<int>(m0) + quarter * 32);
+                }
+              }
               ptx::bulk_commit();
             }
           }
@@ -606,7 +626,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      // TMEM has been read out: hand the accumulator back before the stores drain.
+      if (!released) {
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -615,6 +635,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         } else {
           ptx::mbar_arrive(bar_acc_empty + 8 * acc);
         }
+      }
       }
     }
     if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
