@@ -161,6 +161,13 @@ def _cpu_forward_rate(cfg, batch: int, repeats: int, warmup: int) -> tuple[float
     return batch / med, med * 1e3
 
 
+def _config(batch: int, world: int, mode: str) -> dict:
+    """The workload both arms report (the reference arm times a bounded sample of it on the CPU)."""
+    return {"workload": f"BT4-shape forward (E1024 L15 H32 F1536 smolgen 32->256), batch {batch} per GPU",
+            "batch_per_gpu": batch, "global_batch": batch * world, "mode": mode, "parallelism": f"replicas x{world}",
+            "l2": "working set per step (several GB of activations) far exceeds the 126 MB L2"}
+
+
 def run_reference(args) -> None:
     """The reference arm: the CPU fp32 forward on the host cores (the reference itself has no
     executable forward: it is a graph compiler whose runtime lives outside its tree)."""
@@ -169,6 +176,8 @@ def run_reference(args) -> None:
         return
     from lczero_triton_b200.config import BT4
 
+    # torchrun pins OMP_NUM_THREADS to 1; the CPU arm is meant to use every host core.
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     threads = torch.get_num_threads()
     rate, ms = _cpu_forward_rate(BT4, CPU_SAMPLE_BATCH, max(1, args.steps), max(1, args.warmup))
     sample = f"BT4 fp32 forward, batch {CPU_SAMPLE_BATCH} per step, median of {max(1, args.steps)} steps"
@@ -176,7 +185,8 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": rate, "unit": "positions/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BT4-shape forward (E1024 L15 H32 F1536), CPU fp32 oracle", "batch_per_step": CPU_SAMPLE_BATCH},
+        "config": dict(_config(args.batch, max(1, args.gpus), args.mode),
+                       sample=f"CPU fp32 forward of the same network, {CPU_SAMPLE_BATCH} positions per step"),
         "cpu_baseline": {"value": rate, "unit": "positions/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": "positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -202,15 +212,28 @@ def run(args) -> None:
     masks_h, values_h = masks_h.pin_memory(), values_h.pin_memory()
     masks_d, values_d = masks_h.cuda(), values_h.cuda()
 
-    def step_resident() -> None:
+    def step_eager() -> None:
         net.forward(masks_d, values_d)
 
     # ---- device-resident throughput
-    step_resident()
+    step_eager()
     torch.cuda.synchronize()
     launches_before = _lib.launch_count()
-    step_resident()
+    step_eager()
     launches_per_step = _lib.launch_count() - launches_before
+    step_resident = step_eager
+    graph_error = None
+    if args.graph:
+        # The whole forward as one CUDA graph: the ~220 launches replay without host work in between.
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                net.forward(masks_d, values_d)
+            step_resident = graph.replay
+        except Exception as exc:  # noqa: BLE001 - fall back to eager launches, say so in the line
+            args.graph = 0
+            graph_error = repr(exc)[:160]
     sampler = ClockSampler(local)
     sampler.start()
     total_ms = _timed_steps(step_resident, args.warmup, args.steps, dist)
@@ -240,13 +263,14 @@ def run(args) -> None:
         "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16" if args.mode == "bf16" else "int8", "data": "synthetic",
-        "config": {"workload": f"BT4-shape forward (E1024 L15 H32 F1536 smolgen 32->256), batch {batch} per GPU",
-                   "batch_per_gpu": batch, "global_batch": batch * world, "mode": args.mode, "parallelism": f"replicas x{world}",
-                   "l2": "working set per step (several GB of activations) far exceeds the 126 MB L2"},
+        "config": _config(batch, world, args.mode),
         "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
         "e2e": {"value": e2e_value, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps},
     }
+    line["config"]["launch"] = "CUDA graph replay" if args.graph else "eager launches"
+    if graph_error is not None:
+        line["config"]["graph_error"] = graph_error
     flops = cfg.flops_per_position()
     line["forward_tflops_per_gpu"] = flops * batch / (ms_per_step * 1e-3) / 1e12
     line["forward_frac_of_sustained_bf16_peak"] = line["forward_tflops_per_gpu"] / peaks["bf16_tflops_sustained"]
@@ -278,6 +302,7 @@ def run(args) -> None:
         }
         # ---- CPU baseline beside it (bounded sample of the same workload)
         if not args.no_cpu_baseline:
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
             rate, ms = _cpu_forward_rate(cfg, CPU_SAMPLE_BATCH, 3, 1)
             line["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": torch.get_num_threads(),
                                     "kind": "port", "sample": f"BT4 fp32 forward, batch {CPU_SAMPLE_BATCH}, median of 3 after 1 warm-up ({ms:.0f} ms each)"}
@@ -420,6 +445,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
+    ap.add_argument("--graph", type=int, default=1, help="replay the forward from a CUDA graph in the timed loop")
     ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm"],
                     help="measure one kernel instead of the whole forward pass")
     ap.add_argument("--m", type=int, default=262144)

@@ -15,6 +15,8 @@
 // what the policy head uses.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -28,7 +30,6 @@ constexpr int kBiasStride = 144;     // bytes; 128-byte rows padded so fragment 
 constexpr int kTileBytes = 64 * kRowStride;            // one 64 x 32 bf16 operand tile
 constexpr int kBiasBytes = 64 * kBiasStride;
 constexpr int kStageBytes = 3 * kTileBytes + kBiasBytes;  // 24576
-constexpr int kHeadsPerBlock = 8;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -111,7 +112,10 @@ __device__ __forceinline__ void load_head(uint8_t* stage, const AttnParams& p, l
   }
 }
 
+// HPB = consecutive heads streamed by one CTA.
+template <int HPB>
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
+  constexpr int kHeadsPerBlock = HPB;
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -409,18 +413,26 @@ int attention(void* out, const void* q, const void* k, const void* v, const void
   p.items = batch * heads;
   p.heads = heads;
   p.scale = scale;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kStageBytes) !=
-        cudaSuccess) {
+  // Heads per CTA: long runs amortise the pipeline prologue; short runs keep all SMs busy when the
+  // batch is small.  LC0B200_ATTN_HPB overrides the choice (measurement aid).
+  static const int forced = []() {
+    const char* v = getenv("LC0B200_ATTN_HPB");
+    return v != nullptr ? atoi(v) : 0;
+  }();
+  int hpb = forced != 0 ? forced : (p.items >= 64LL * 8 * sm_count() ? 16 : (p.items >= 16LL * 8 * sm_count() ? 8 : 4));
+  auto run = [&](auto kernel, int heads_per_block) -> int {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kStageBytes) != cudaSuccess) {
       return LC0B200_ERR_CUDA;
     }
-    configured = true;
-  }
-  const long long blocks = ceil_div_ll(p.items, kHeadsPerBlock);
-  if (blocks > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
-  attention_kernel<<<static_cast<unsigned>(blocks), 128, 2 * kStageBytes, st>>>(p);
-  return launch_status();
+    const long long blocks = ceil_div_ll(p.items, heads_per_block);
+    if (blocks > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
+    kernel<<<static_cast<unsigned>(blocks), 128, 2 * kStageBytes, st>>>(p);
+    return launch_status();
+  };
+  if (hpb >= 32) return run(attention_kernel<32>, 32);
+  if (hpb >= 16) return run(attention_kernel<16>, 16);
+  if (hpb >= 8) return run(attention_kernel<8>, 8);
+  return run(attention_kernel<4>, 4);
 }
 
 int batched_matmul(void* out, const void* a, const void* b, const void* scale, int operation, long long batch_count,

@@ -45,7 +45,10 @@ constexpr int kGroupBytes = 32 * kRowBytes;  // staging for 32 rows x 64 bf16 co
 //   kRes  : y = alpha * (dequant(acc) + bias) + skip, skip plain or a deferred LayerNorm; row sums out
 enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 
-template <int BN, int CTAS, int MODE>
+// SETS = 2 keeps two sets of staging buffers and alternates them tile by tile, so that a tile's
+// stores never have to be waited for by the next tile.  Used for short-K problems, where the
+// epilogue, not the main loop, sets the pace and few pipeline stages are needed.
+template <int BN, int CTAS, int MODE, int SETS = 1>
 struct TileCfg {
   static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
   static constexpr int kABytes = kBM * kRowBytes;
@@ -61,7 +64,8 @@ struct TileCfg {
   // One staging buffer per warp and 64-column group: the residual flavour prefetches the skip
   // operand of the whole tile into them, and every flavour can fill one buffer while the TMA store
   // of the other is still reading it.
-  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups;
+  static constexpr int kSets = kTmaStore ? SETS : 1;
+  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups * kSets;
   static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
   static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 512 /*barriers*/;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
@@ -264,12 +268,12 @@ __device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* 
   return __uint_as_float(raw);
 }
 
-template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
-__global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE>::kThreads, 1)
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS>
+__global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE, SETS>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_skip,
                     const KernelParams p) {
-  using Cfg = TileCfg<BN, CTAS, MODE>;
+  using Cfg = TileCfg<BN, CTAS, MODE, SETS>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
   constexpr int kUmmaK = INT8 ? 32 : 16;          // K per tcgen05.mma (32 bytes)
@@ -427,7 +431,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int half = ew >> 2;                  // which share of the tile's columns (eight-warp layout)
     constexpr int kColsPerWarp = Cfg::kColsPerWarp;
     const int row_in_tile = quarter * 32 + lane;
-    const uint32_t staging = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
+    const uint32_t staging_warp = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
     const uint32_t skip_bar = bar_skip + 8 * ew;
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;
     uint32_t local = 0;
@@ -440,6 +444,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t acc_phase = (local >> 1) & 1u;
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.m;
+      const uint32_t staging = staging_warp + (Cfg::kSets == 2 ? (local & 1u) : 0u) * Cfg::kGroups * kGroupBytes;
 
       // ---- everything that can be fetched before the accumulator is complete
       RowCtx rc;
@@ -459,7 +464,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (tma_path) {
         // The staging buffers are free once the previous tile's stores have finished reading them;
         // those were issued a whole main loop ago, so this wait is normally already satisfied.
-        if (lane == 0) ptx::bulk_wait_read<0>();
+        // (With two sets the buffers were last used two tiles ago: one younger group may be in flight.)
+        if (lane == 0) ptx::bulk_wait_read<Cfg::kSets - 1>();
         __syncwarp();
       }
       if constexpr (MODE == kRes) {
@@ -702,9 +708,9 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS = 1>
 int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
-  using Cfg = TileCfg<BN, CTAS, MODE>;
+  using Cfg = TileCfg<BN, CTAS, MODE, SETS>;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;
   constexpr int kPanelN = INT8 ? 128 : 64;
   const int eb = INT8 ? 1 : 2;
@@ -725,7 +731,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
     if (!aligned16(g.res_skip_bf16) || (g.ld_skip % 8) != 0) return LC0B200_ERR_MISALIGNED;
     if (!make_map(&map_skip, g.res_skip_bf16, 2, g.m, g.n, g.ld_skip, 32, 64)) return LC0B200_ERR_CUDA;
   }
-  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE>;
+  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE, SETS>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -795,6 +801,12 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   // (64 bf16 or 128 int8 columns); narrower outputs just run a partly empty tile.
   constexpr int kMinBn = W_KN ? (INT8 ? 128 : 64) : 32;
   if (g.n > 128) {
+    if constexpr (MODE == kPlain && !INT8 && !W_KN) {
+      // Short K: the epilogue sets the pace; trade pipeline stages for a second set of staging buffers.
+      if (g.m >= kPairMinRows && g.k <= 512 && pair_kernels_enabled()) {
+        return launch<256, INT8, W_KN, 2, MODE, 2>(g, stream);
+      }
+    }
     if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
