@@ -276,29 +276,48 @@ def run(args) -> None:
     line["forward_frac_of_sustained_bf16_peak"] = line["forward_tflops_per_gpu"] / peaks["bf16_tflops_sustained"]
 
     if rank == 0 and world == 1:
-        # ---- roofline of the dominant kernel: the QKV projection GEMM (tcgen05), timed alone
+        # ---- roofline of the dominant kernel: the QKV projection GEMM (tcgen05), timed alone, in the
+        # form the forward pass launches it (bf16: LayerNorm of the input rows folded into the epilogue)
         from lczero_triton_b200 import ops
 
         t_rows = batch * 64
-        layer = net.layers[0]["qkv"]
-        a = torch.randn((t_rows, cfg.embedding), device="cuda").to(torch.bfloat16)
-        out = torch.empty((t_rows, layer.n), dtype=torch.bfloat16, device="cuda")
         if args.mode == "int8":
+            layer = net.layers[0]["qkv"]
             a = torch.randint(-127, 128, (t_rows, cfg.embedding), device="cuda", dtype=torch.int8)
+            extra = {"bias": layer.bias, "col_scale": layer.col_scale,
+                     "row_scale": torch.rand(t_rows, device="cuda") * 0.01 + 0.001}
+            kernel_name = "gemm_tcgen05_kernel<256, int8, NK, pair, plain>"
+        else:
+            layer = net.layers[0]["qkv_f"] if net.deferred else net.layers[0]["qkv"]
+            a = torch.randn((t_rows, cfg.embedding), device="cuda").to(torch.bfloat16)
+            if net.deferred:
+                parts = (cfg.embedding + 63) // 64
+                stats = torch.rand((parts, t_rows, 2), device="cuda") + 1.0
+                extra = {"ln_in": (stats, layer.fold_c, layer.fold_d)}
+                kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, ln_in>"
+            else:
+                extra = {"bias": layer.bias}
+                kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, plain>"
+        out = torch.empty((t_rows, layer.n), dtype=torch.bfloat16, device="cuda")
 
         def gemm_once() -> None:
-            ops.gemm(out, a, layer.w, m=t_rows, n=layer.n, k=layer.k, bias=layer.bias, w_layout=layer.layout,
-                     col_scale=layer.col_scale)
+            ops.gemm(out, a, layer.w, m=t_rows, n=layer.n, k=layer.k, w_layout=layer.layout, **extra)
 
         gemm_ms = _timed_steps(gemm_once, 3, 10, None) / 10
         gemm_flops = 2.0 * t_rows * layer.n * layer.k
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"] * (2.0 if args.mode == "int8" else 1.0)
+        # DRAM traffic of this kernel from one ncu capture at 32768 rows (profiles/gemm_tcgen05_*_m32768.md),
+        # scaled by the row count: the traffic is A + C, both proportional to the rows.
+        traffic_per_row = (226.28e6 if args.mode == "bf16" else 178.52e6) / 32768.0
         line["roofline"] = {
-            "bound": "tensor", "kernel": "gemm_tcgen05_kernel (QKV projection, M=%d N=%d K=%d)" % (t_rows, layer.n, layer.k),
+            "bound": "tensor", "kernel": "%s (QKV projection, M=%d N=%d K=%d)" % (kernel_name, t_rows, layer.n, layer.k),
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "peak_source": f"{peak_kind} burst bf16" + (" x2 nominal for int8" if args.mode == "int8" else ""),
-            "ms_per_launch": gemm_ms, "traffic": None,
+            "frac_of_sustained_peak": achieved / (peaks["bf16_tflops_sustained"] * (2.0 if args.mode == "int8" else 1.0)),
+            "ms_per_launch": gemm_ms, "flops_per_launch": gemm_flops,
+            "traffic": traffic_per_row * t_rows,
+            "traffic_source": "ncu dram__bytes_read+write at 32768 rows, scaled by rows",
         }
         # ---- CPU baseline beside it (bounded sample of the same workload)
         if not args.no_cpu_baseline:

@@ -177,8 +177,9 @@ LC0B200_API int lc0b200_transpose(void* dst, const void* src, int rows, int cols
  * T/test_layer_norm.py:412-415): v = act(in + bias); if has_skip v = alpha*v + skip;
  * out = (v - mean) / sqrt(var + epsilon) * gamma + beta, population variance, fp32 math.
  * alpha points at one bf16 element.  skip / alpha may be NULL when has_skip == 0.
- * If q_out_int8 and q_scale_f32 are non-NULL the normalised row is additionally quantised
- * per row (see lc0b200_quantize_rows) — no reference counterpart. */
+ * If q_out_int8 and q_scale_f32 are non-NULL the normalised row (as rounded to bf16) is additionally
+ * quantised per row (see lc0b200_quantize_rows) — no reference counterpart; out_bf16 may then be
+ * NULL to store the quantised form only. */
 LC0B200_API int lc0b200_layer_norm(void* out_bf16, const void* in_bf16, const void* bias_bf16, const void* skip_bf16,
                        const void* gamma_bf16, const void* beta_bf16, const void* alpha_bf16,
                        long long row_count, int width, int activation, int has_skip, float epsilon,

@@ -262,9 +262,10 @@ LC0B200_API int lc0b200_transpose(void* dst, const void* src, int rows, int cols
 LC0B200_API int lc0b200_layer_norm(void* out, const void* in, const void* bias, const void* skip, const void* gamma,
                        const void* beta, const void* alpha, long long row_count, int width, int activation,
                        int has_skip, float epsilon, void* q_out, float* q_scale, void* stream) {
-  REQUIRE_PTR(out); REQUIRE_PTR(in); REQUIRE_PTR(bias); REQUIRE_PTR(gamma); REQUIRE_PTR(beta);
+  REQUIRE_PTR(in); REQUIRE_PTR(bias); REQUIRE_PTR(gamma); REQUIRE_PTR(beta);
   if (has_skip) { REQUIRE_PTR(skip); REQUIRE_PTR(alpha); }
   if ((q_out == nullptr) != (q_scale == nullptr)) return LC0B200_ERR_NULL_POINTER;
+  if (out == nullptr && q_out == nullptr) return LC0B200_ERR_NULL_POINTER;  // out may be NULL only with q_out
   REQUIRE_SHAPE(row_count >= 0 && width > 0 && epsilon >= 0.0f);
   if (activation != LC0B200_ACT_NONE && activation != LC0B200_ACT_MISH && activation != LC0B200_ACT_SWISH) {
     return LC0B200_ERR_UNSUPPORTED;

@@ -832,8 +832,16 @@ int dispatch_mode(const lc0b200_gemm_args& g, cudaStream_t stream) {
   if ((ln_in || res || g.stats_out != nullptr) && g.out_kind != LC0B200_OUT_BF16) return LC0B200_ERR_UNSUPPORTED;
   if (g.stats_out != nullptr && !res) return LC0B200_ERR_UNSUPPORTED;
   if constexpr (INT8) {
-    // The deferred-LayerNorm epilogues are instantiated for bf16 operands only.
-    if (ln_in || res) return LC0B200_ERR_UNSUPPORTED;
+    // An int8 GEMM cannot fold the LayerNorm of its input (the input is already quantised); it can
+    // produce the residual form.  Only the pre-transposed weight layout is instantiated for it.
+    if (ln_in) return LC0B200_ERR_UNSUPPORTED;
+    if (res) {
+      if constexpr (W_KN) {
+        return LC0B200_ERR_UNSUPPORTED;
+      } else {
+        return dispatch_bn<INT8, W_KN, kRes>(g, stream);
+      }
+    }
     return dispatch_bn<INT8, W_KN, kPlain>(g, stream);
   } else {
     if (ln_in) return dispatch_bn<INT8, W_KN, kLnIn>(g, stream);

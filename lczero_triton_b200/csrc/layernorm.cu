@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(co
         v[g][2 * j + 1] = r.y;
         amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
       }
-      out[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+      if (p.out != nullptr) out[idx] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
   if (p.q_out != nullptr) {
@@ -309,6 +309,7 @@ int layer_norm(void* out, const void* in, const void* bias, const void* skip, co
   p.activation = activation;
   p.has_skip = has_skip;
   p.epsilon = epsilon;
+  if (out == nullptr && q_out == nullptr) return LC0B200_ERR_NULL_POINTER;
   const bool vec = (width % 8 == 0) && width <= 256 * kMaxGroups && aligned16(out) && aligned16(in) &&
                    aligned16(bias) && aligned16(gamma) && aligned16(beta) && (!has_skip || aligned16(skip)) &&
                    (q_out == nullptr || aligned16(q_out));

@@ -74,9 +74,9 @@ class Bt4Net:
             self.device = torch.device("cuda", torch.cuda.current_device())
         # bf16 mode keeps the residual stream un-normalised between GEMMs ("deferred LayerNorm"): the
         # two LayerNorm launches per encoder layer become epilogue arithmetic (see lc0b200_gemm_args).
+        # (Available for int8 too, but there the short int8 main loop cannot hide the heavier epilogue
+        # and the stand-alone LayerNorm path measures faster, so it is off by default.)
         self.deferred = (mode == "bf16") if deferred_layer_norm is None else bool(deferred_layer_norm)
-        if self.deferred and mode != "bf16":
-            raise ValueError("deferred LayerNorm is implemented for the bf16 mode only")
         self._layout = _lib.W_NK if weight_layout == "nk" else _lib.W_KN
         self._w = {k: v.to(device=self.device, dtype=torch.bfloat16).contiguous() for k, v in weights.items()}
         self._scalars = {k: float(v.float().reshape(-1)[0]) for k, v in weights.items() if v.numel() == 1}
@@ -155,13 +155,14 @@ class Bt4Net:
             for i, layer in enumerate(self.layers):
                 p = f"/encoder{i}"
                 prev = "/attn_body/ln2" if i == 0 else f"/encoder{i - 1}/ln2"
-                layer["qkv_f"] = self._dense_folded([f"{p}/mha/Q/w/w", f"{p}/mha/K/w/w", f"{p}/mha/V/w/w"],
-                                                    [f"{p}/mha/Q/b/w", f"{p}/mha/K/b/w", f"{p}/mha/V/b/w"],
-                                                    f"{prev}/w/scale", f"{prev}/w/bias")
                 layer["compress_f"] = self._dense_folded([f"{p}/smolgen/compress/w"], None,
                                                          f"{prev}/w/scale", f"{prev}/w/bias")
-                layer["ffn1_f"] = self._dense_folded([f"{p}/ffn/dense1/w/w"], [f"{p}/ffn/dense1/b/w"],
-                                                     f"{p}/ln1/w/scale", f"{p}/ln1/w/bias")
+                if not q8:  # the int8 GEMMs read a quantised LayerNorm output instead of folding it
+                    layer["qkv_f"] = self._dense_folded([f"{p}/mha/Q/w/w", f"{p}/mha/K/w/w", f"{p}/mha/V/w/w"],
+                                                        [f"{p}/mha/Q/b/w", f"{p}/mha/K/b/w", f"{p}/mha/V/b/w"],
+                                                        f"{prev}/w/scale", f"{prev}/w/bias")
+                    layer["ffn1_f"] = self._dense_folded([f"{p}/ffn/dense1/w/w"], [f"{p}/ffn/dense1/b/w"],
+                                                         f"{p}/ln1/w/scale", f"{p}/ln1/w/bias")
                 layer["out_b"] = self._w[f"{p}/mha/out/dense/b/w"]
                 layer["ffn2_b"] = self._w[f"{p}/ffn/dense2/b/w"]
         self.pol1 = d("/policy/dense1/matmul/w", "/policy/dense1/add/w")
@@ -312,10 +313,17 @@ class Bt4Net:
         d = c.embedding
         eps = c.ln_eps
         w = self._w
+        q8 = self.mode == "int8"
+        qd, qf, qs = (ws["q_d"], ws["q_f"], ws["q_scale"]) if q8 else (None, None, None)
 
         def materialise(z: torch.Tensor, ln: str, out: torch.Tensor) -> torch.Tensor:
             return ops.layer_norm(out, z, self.zero_bias, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], row_count=t, width=d,
                                   epsilon=eps)
+
+        def normalise_and_quantise(z: torch.Tensor, ln: str) -> None:
+            """int8 mode: LayerNorm(z) straight to per-row int8 (no bf16 copy is stored)."""
+            ops.layer_norm(None, z, self.zero_bias, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], row_count=t, width=d,
+                           epsilon=eps, q_out=qd, q_scale=qs)
 
         # embedding FFN tail: z = alpha * (hidden @ W2 + b2) + skip   (skip is a plain tensor here)
         z, stats, ln = ws["x1"], ws["stats0"], "/attn_body/ln2"
@@ -328,18 +336,34 @@ class Bt4Net:
         free_s = [ws["stats1"], ws["stats2"]]
         for i, layer in enumerate(self.layers):
             p = f"/encoder{i}"
-            self._gemm_folded(ws["qkv"], z, layer["qkv_f"], t, stats)
+            if q8:
+                normalise_and_quantise(z, ln)
+                self._gemm(ws["qkv"], qd, layer["qkv"], t, row_scale=qs)
+            else:
+                self._gemm_folded(ws["qkv"], z, layer["qkv_f"], t, stats)
             self._gemm_folded(ws["compressed"], z, layer["compress_f"], t, stats)
             self._smolgen_and_attention(ws, layer, i, b)
             z1, stats1 = free_z[0], free_s[0]
-            ops.gemm(z1, ws["merged"], layer["out"].w, m=t, n=d, k=d, bias=layer["out_b"], w_layout=layer["out"].layout,
+            a_out, scale_out = ws["merged"], None
+            if q8:
+                ops.quantize_rows(qd, qs, ws["merged"], t, d)
+                a_out, scale_out = qd, qs
+            ops.gemm(z1, a_out, layer["out"].w, m=t, n=d, k=d, bias=layer["out_b"], w_layout=layer["out"].layout,
+                     row_scale=scale_out, col_scale=layer["out"].col_scale,
                      res_skip=z, res_ln=(stats, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"]),
                      res_alpha=self._scalars[f"{p}/alpha*input/w"], stats_out=stats1, ln_eps=eps)
-            self._gemm_folded(ws["hidden"], z1, layer["ffn1_f"], t, stats1, activation="mish")
+            a_ffn2, scale_ffn2 = ws["hidden"], None
+            if q8:
+                normalise_and_quantise(z1, f"{p}/ln1")
+                self._gemm(ws["hidden"], qd, layer["ffn1"], t, activation="mish", row_scale=qs)
+                ops.quantize_rows(qf, qs, ws["hidden"], t, c.ffn)
+                a_ffn2, scale_ffn2 = qf, qs
+            else:
+                self._gemm_folded(ws["hidden"], z1, layer["ffn1_f"], t, stats1, activation="mish")
             z2, stats2 = free_z[1], free_s[1]
-            ops.gemm(z2, ws["hidden"], layer["ffn2"].w, m=t, n=d, k=c.ffn, bias=layer["ffn2_b"],
-                     w_layout=layer["ffn2"].layout, res_skip=z1,
-                     res_ln=(stats1, w[f"{p}/ln1/w/scale"], w[f"{p}/ln1/w/bias"]),
+            ops.gemm(z2, a_ffn2, layer["ffn2"].w, m=t, n=d, k=c.ffn, bias=layer["ffn2_b"],
+                     w_layout=layer["ffn2"].layout, row_scale=scale_ffn2, col_scale=layer["ffn2"].col_scale,
+                     res_skip=z1, res_ln=(stats1, w[f"{p}/ln1/w/scale"], w[f"{p}/ln1/w/bias"]),
                      res_alpha=self._scalars[f"{p}/ffn/alpha/w"], stats_out=stats2, ln_eps=eps)
             free_z, free_s = [z, z1], [stats, stats1]
             z, stats, ln = z2, stats2, f"{p}/ln2"

@@ -165,7 +165,7 @@ def transpose(dst: torch.Tensor, src: torch.Tensor, rows: int, cols: int) -> tor
     return dst
 
 
-def layer_norm(out: torch.Tensor, x: torch.Tensor, bias: torch.Tensor, gammas: torch.Tensor, betas: torch.Tensor, *,
+def layer_norm(out: torch.Tensor | None, x: torch.Tensor, bias: torch.Tensor, gammas: torch.Tensor, betas: torch.Tensor, *,
                row_count: int, width: int, activation: str = "none", epsilon: float = 1e-3,
                skip: torch.Tensor | None = None, alpha: torch.Tensor | None = None,
                q_out: torch.Tensor | None = None, q_scale: torch.Tensor | None = None) -> torch.Tensor:

@@ -109,11 +109,12 @@ def test_positions_are_independent(pkg) -> None:
         assert torch.equal(f[8:], h)
 
 
+@pytest.mark.parametrize("deferred", [True, False], ids=["deferred-ln", "standalone-ln"])
 @pytest.mark.parametrize("name", ["TINY", "BT4"])
-def test_int8_network_tracks_int8_oracle(pkg, name) -> None:
+def test_int8_network_tracks_int8_oracle(pkg, name, deferred) -> None:
     cfg = getattr(pkg["config"], name)
     batch = 4
-    weights, masks, values, got, taps = _run(pkg, cfg, batch, mode="int8")
+    weights, masks, values, got, taps = _run(pkg, cfg, batch, mode="int8", deferred=deferred)
     want_taps: dict[str, torch.Tensor] = {}
     want = O.forward(weights, cfg, masks, values, table=pkg["table"], taps=want_taps, int8=True,
                      round_to=torch.bfloat16)

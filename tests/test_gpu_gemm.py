@@ -224,6 +224,46 @@ def test_deferred_layer_norm_epilogues(ops, m) -> None:
     torch.testing.assert_close(hidden.float().cpu(), want_h, rtol=2e-2, atol=2e-2)
 
 
+def test_int8_gemm_residual_epilogue(ops) -> None:
+    """The residual form on the int8 GEMM: z = alpha * (dequant(Aq Wq) + b) + LN(z_prev), with row sums."""
+    from lczero_triton_b200 import _lib
+
+    m, d, f, eps, alpha = 8300, 1024, 1536, 1e-3, 0.4273
+    g = _gen(180)
+    z_prev = (torch.randn((m, d), generator=g) * 1.3 + 0.2).to(BF16)
+    gamma, beta = (1 + 0.1 * torch.randn(d, generator=g)).to(BF16), (0.1 * torch.randn(d, generator=g)).to(BF16)
+    a = torch.randn((m, f), generator=g).to(BF16)
+    w = (torch.randn((f, d), generator=g) * 0.02).to(BF16)
+    bias = (torch.randn(d, generator=g) * 0.1).to(BF16)
+    aq, s_a = int8_oracle.quantize_rows(a)
+    wq, s_w = int8_oracle.quantize_weight(w)
+    branch = int8_oracle.dequant(int8_oracle.int_matmul(aq, wq), s_a, s_w, bias)
+    want = alpha * branch + O.layer_norm(z_prev, torch.zeros(d), gamma, beta, "none", eps)
+    z = torch.empty((m, d), dtype=BF16, device="cuda")
+    stats = torch.empty((d // 64, m, 2), dtype=torch.float32, device="cuda")
+    ops.gemm(z, aq.cuda(), wq.t().contiguous().cuda(), m=m, n=d, k=f, bias=bias.cuda(), w_layout=_lib.W_NK,
+             row_scale=s_a.cuda(), col_scale=s_w.cuda(), res_skip=z_prev.cuda(),
+             res_ln=(_partial_stats(z_prev).cuda(), gamma.cuda(), beta.cuda()), res_alpha=alpha, stats_out=stats,
+             ln_eps=eps)
+    torch.testing.assert_close(z.float().cpu(), want, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(stats.cpu(), _partial_stats(z.cpu()), rtol=1e-4, atol=1e-3)
+
+
+def test_layer_norm_to_int8_only(ops) -> None:
+    """LayerNorm straight to per-row int8, no bf16 copy stored (out == NULL)."""
+    rows, width = 37, 1024
+    x = torch.randn((rows, width), generator=_gen(181)).to(BF16)
+    bias, gamma, beta = (torch.randn(width, generator=_gen(182 + i)).mul(0.2).to(BF16) for i in range(3))
+    both = torch.empty_like(x, device="cuda")
+    q1, s1 = torch.empty((rows, width), dtype=torch.int8, device="cuda"), torch.empty(rows, device="cuda")
+    q2, s2 = torch.empty_like(q1), torch.empty_like(s1)
+    ops.layer_norm(both, x.cuda(), bias.cuda(), gamma.cuda(), beta.cuda(), row_count=rows, width=width, q_out=q1, q_scale=s1)
+    ops.layer_norm(None, x.cuda(), bias.cuda(), gamma.cuda(), beta.cuda(), row_count=rows, width=width, q_out=q2, q_scale=s2)
+    assert torch.equal(q1, q2) and torch.equal(s1, s2)
+    want_q, want_s = int8_oracle.quantize_rows(both.cpu())
+    assert torch.equal(q2.cpu(), want_q) and torch.equal(s2.cpu(), want_s)
+
+
 def test_gemm_linearity_at_full_size(ops) -> None:
     """Size-independent property at the benchmark's row count: GEMM(a1 + a2) = GEMM(a1) + GEMM(a2)
     when the sums are exact in bf16 (small integers), checked on sampled rows of a 262144-row problem."""
