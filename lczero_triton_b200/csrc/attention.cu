@@ -400,6 +400,9 @@ int softmax_64(void* out, const void* qk, const void* smolgen, long long rows, c
 int attention(void* out, const void* q, const void* k, const void* v, const void* bias, float scale,
               long long batch, int heads, long long ldq, long long ldk, long long ldv, long long ldo,
               cudaStream_t st) {
+  if (attention_tc_supported(out, q, k, v, bias, batch, heads, ldq, ldk, ldv, ldo)) {
+    return attention_tc(out, q, k, v, bias, scale, batch, heads, ldq, ldk, ldv, ldo, st);
+  }
   AttnParams p;
   p.out = reinterpret_cast<bf16*>(out);
   p.q = reinterpret_cast<const bf16*>(q);

@@ -30,6 +30,7 @@
 #include "common.cuh"
 #include "gemm.h"
 #include "ptx.cuh"
+#include "tensormap.h"
 
 namespace lc0b200 {
 
@@ -674,38 +675,12 @@ bool pair_kernels_enabled() {
   return enabled;
 }
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess) {
-      return nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(sym);
-  }();
-  return fn;
-}
-
 // 2-D row-major tensor [rows, cols] with a row pitch, tiled into [box_rows, box_cols] boxes
 // whose inner extent is exactly 128 bytes (the swizzle span).
 bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows, long long cols,
               long long pitch_elems, int box_rows, int box_cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * elem_bytes};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  return make_tensormap_2d(map, base, elem_bytes, rows, cols, pitch_elems, box_rows, box_cols,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS = 1>

@@ -46,6 +46,13 @@ int attention(void* out, const void* q, const void* k, const void* v, const void
 int batched_matmul(void* out, const void* a, const void* b, const void* scale, int operation, long long batch_count,
                    int m, int n, int k, int heads, cudaStream_t st);
 
+// attention_tc.cu: the same operator on tcgen05 / TMEM (pairs of heads; needs an even head count)
+bool attention_tc_supported(const void* out, const void* q, const void* k, const void* v, const void* bias,
+                            long long batch, int heads, long long ldq, long long ldk, long long ldv, long long ldo);
+int attention_tc(void* out, const void* q, const void* k, const void* v, const void* bias, float scale,
+                 long long batch, int heads, long long ldq, long long ldk, long long ldv, long long ldo,
+                 cudaStream_t st);
+
 // policy.cu
 int promotion_logits(void* records, const void* keys, const void* w, int batch, int width, cudaStream_t st);
 int policy_tail(float* out, const void* records, const void* keys, const void* w, const int32_t* table, int batch,
