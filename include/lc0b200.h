@@ -245,6 +245,14 @@ LC0B200_API int lc0b200_embed_concat(void* emb_in_bf16, const uint64_t* masks, c
 LC0B200_API int lc0b200_policy_tail(float* out_f32, const void* records_bf16, const void* keys_bf16, const void* w_bf16,
                         const int32_t* table, int batch_size, int width, void* stream);
 
+/* The step right after the path in lc0 (BT4_PLAN.md:42-43: the graph emits raw WDL logits and the
+ * runtime applies the softmax on the host): wdl_probs = softmax(wdl_logits) over 3, policy_probs =
+ * softmax of the policy logits over the legal moves only (legal_mask[b,o] != 0; NULL = all legal;
+ * illegal entries get 0; a position without legal moves gets all zeros).  Either output may be NULL. */
+LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits,
+                                 const float* wdl_logits, const uint8_t* legal_mask, int batch_size,
+                                 int policy_size, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,7 @@ SIGNATURES: dict[str, tuple] = {
     "lc0b200_embed_position_input": (_P, _P, _P, _I, _P),
     "lc0b200_embed_concat": (_P, _P, _P, _P, _I, _I, _P),
     "lc0b200_policy_tail": (_P, _P, _P, _P, _P, _I, _I, _P),
+    "lc0b200_output_probabilities": (_P, _P, _P, _P, _P, _I, _I, _P),
 }
 STRING_GETTERS = ("lc0b200_version", "lc0b200_status_string")
 

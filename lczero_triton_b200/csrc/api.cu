@@ -351,4 +351,16 @@ LC0B200_API int lc0b200_policy_tail(float* out, const void* records, const void*
   return policy_tail(out, records, keys, w, table, batch_size, width, S(stream));
 }
 
+LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits,
+                                             const float* wdl_logits, const uint8_t* legal_mask, int batch_size,
+                                             int policy_size, void* stream) {
+  if (policy_probs == nullptr && wdl_probs == nullptr) return LC0B200_ERR_NULL_POINTER;
+  if (policy_probs != nullptr) REQUIRE_PTR(policy_logits);
+  if (wdl_probs != nullptr) REQUIRE_PTR(wdl_logits);
+  REQUIRE_SHAPE(batch_size >= 0 && policy_size > 0);
+  if (batch_size == 0) return LC0B200_OK;
+  return output_probabilities(policy_probs, wdl_probs, policy_logits, wdl_logits, legal_mask, batch_size, policy_size,
+                              S(stream));
+}
+
 }  // extern "C"

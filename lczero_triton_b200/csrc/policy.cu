@@ -77,7 +77,73 @@ __global__ void __launch_bounds__(256) policy_tail_kernel(float* __restrict__ ou
   }
 }
 
+// Output probabilities: WDL softmax and policy softmax over the legal moves, one CTA per position.
+__global__ void __launch_bounds__(256) output_probabilities_kernel(float* __restrict__ policy_probs,
+                                                                   float* __restrict__ wdl_probs,
+                                                                   const float* __restrict__ policy_logits,
+                                                                   const float* __restrict__ wdl_logits,
+                                                                   const uint8_t* __restrict__ legal, int policy_size) {
+  __shared__ float red[8];
+  __shared__ float bcast;
+  const long long b = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (wdl_probs != nullptr && threadIdx.x == 0) {
+    const float w = wdl_logits[b * 3], d = wdl_logits[b * 3 + 1], l = wdl_logits[b * 3 + 2];
+    const float m = fmaxf(w, fmaxf(d, l));
+    const float ew = expf(w - m), ed = expf(d - m), el = expf(l - m);
+    const float inv = 1.0f / (ew + ed + el);
+    wdl_probs[b * 3] = ew * inv;
+    wdl_probs[b * 3 + 1] = ed * inv;
+    wdl_probs[b * 3 + 2] = el * inv;
+  }
+  if (policy_probs == nullptr) return;
+  const float* logits = policy_logits + b * policy_size;
+  const uint8_t* mask = legal != nullptr ? legal + b * policy_size : nullptr;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < policy_size; i += 256) {
+    if (mask == nullptr || mask[i] != 0) mx = fmaxf(mx, logits[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = red[0];
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    bcast = m;
+  }
+  __syncthreads();
+  mx = bcast;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < policy_size; i += 256) {
+    if (mask == nullptr || mask[i] != 0) sum += expf(logits[i] - mx);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    bcast = t > 0.0f ? 1.0f / t : 0.0f;
+  }
+  __syncthreads();
+  const float inv = bcast;
+  for (int i = threadIdx.x; i < policy_size; i += 256) {
+    const bool on = mask == nullptr || mask[i] != 0;
+    policy_probs[b * policy_size + i] = (on && inv > 0.0f) ? expf(logits[i] - mx) * inv : 0.0f;
+  }
+}
+
 }  // namespace
+
+int output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits, const float* wdl_logits,
+                         const uint8_t* legal, int batch, int policy_size, cudaStream_t st) {
+  output_probabilities_kernel<<<batch, 256, 0, st>>>(policy_probs, wdl_probs, policy_logits, wdl_logits, legal,
+                                                     policy_size);
+  return launch_status();
+}
 
 int promotion_logits(void* records, const void* keys, const void* w, int batch, int width, cudaStream_t st) {
   promotion_logits_kernel<<<batch, 256, 0, st>>>(reinterpret_cast<bf16*>(records), reinterpret_cast<const bf16*>(keys),

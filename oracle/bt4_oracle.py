@@ -188,6 +188,18 @@ def policy_map(records: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return torch.where(valid[None, :], gathered, torch.zeros((), dtype=records.dtype))
 
 
+def output_probabilities(policy_logits: torch.Tensor, wdl_logits: torch.Tensor,
+                         legal_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """What lc0 does right after the graph (BT4_PLAN.md:42-43: the graph emits raw WDL logits, the
+    softmax is applied on the host): WDL softmax, and the policy softmax over the legal moves only."""
+    wdl = torch.softmax(wdl_logits.float(), dim=-1)
+    logits = policy_logits.float()
+    if legal_mask is not None:
+        logits = torch.where(legal_mask != 0, logits, torch.full_like(logits, float("-inf")))
+    policy = torch.softmax(logits, dim=-1)
+    return torch.nan_to_num(policy, nan=0.0), wdl
+
+
 # --------------------------------------------------------------------------- whole network
 
 def forward(weights: Mapping[str, torch.Tensor], cfg, masks: torch.Tensor, values: torch.Tensor, *,

@@ -400,3 +400,18 @@ def test_policy_tail_equals_promotion_plus_gather(ops) -> None:
     _close(out, O.policy_map(full, table), rtol=1e-2, atol=1e-2)
     plain = table < 4096
     assert torch.equal(out.cpu()[:, plain], rec.float()[:, table[plain].long()])
+
+
+def test_output_probabilities_over_legal_moves(ops) -> None:
+    batch = 5
+    logits = torch.randn((batch, 1858), generator=_gen(90)) * 2
+    wdl = torch.randn((batch, 3), generator=_gen(91))
+    legal = (torch.rand((batch, 1858), generator=_gen(92)) < 0.02).to(torch.uint8)
+    legal[3] = 0  # a position without legal moves
+    policy, wdl_probs = ops.output_probabilities(logits.cuda(), wdl.cuda(), legal.cuda())
+    want_policy, want_wdl = O.output_probabilities(logits, wdl, legal)
+    torch.testing.assert_close(policy.cpu(), want_policy, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(wdl_probs.cpu(), want_wdl, rtol=1e-5, atol=1e-7)
+    assert policy[3].abs().sum() == 0 and (policy.cpu()[legal == 0] == 0).all()
+    everything, _ = ops.output_probabilities(logits.cuda(), wdl.cuda(), None)
+    torch.testing.assert_close(everything.cpu(), torch.softmax(logits, dim=-1), rtol=1e-5, atol=1e-7)
