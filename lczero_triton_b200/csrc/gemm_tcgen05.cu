@@ -772,10 +772,17 @@ constexpr long long kPairMinRows = 8192;
 
 template <bool INT8, bool W_KN, int MODE>
 int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
-  // MN-major weight staging needs BN to be a whole number of 128-byte panels
-  // (64 bf16 or 128 int8 columns); narrower outputs just run a partly empty tile.
-  constexpr int kMinBn = W_KN ? (INT8 ? 128 : 64) : 32;
-  if (g.n > 128) {
+  // Tile width: the widest of 256 / 128 / 64 / 32 that still gives most SMs a tile, so that small
+  // problems (batch 64: a 64 x 256 output) spread over several CTAs instead of one.
+  // MN-major weight staging needs whole 128-byte panels (64 bf16 or 128 int8 columns); the residual
+  // epilogue needs the TMA-store layout (BN >= 128).
+  constexpr int kMinBn = (MODE == kRes) ? 128 : (W_KN ? (INT8 ? 128 : 64) : 32);
+  const long long rows128 = ceil_div_ll(g.m, kBM);
+  const long long enough = sm_count() * 3LL / 5;
+  auto tiles = [&](int bn) { return rows128 * ceil_div_ll(g.n, bn); };
+  int bn = 256;
+  while (bn > kMinBn && (bn / 2 >= g.n || tiles(bn) < enough)) bn /= 2;
+  if (bn == 256) {
     if constexpr (MODE == kPlain && !INT8 && !W_KN) {
       // Short K: the epilogue sets the pace; trade pipeline stages for a second set of staging buffers.
       if (g.m >= kPairMinRows && g.k <= 512 && pair_kernels_enabled()) {
@@ -786,15 +793,13 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
   if constexpr (kMinBn <= 128) {
-    if (g.n > 64 || kMinBn == 128) return launch<128, INT8, W_KN, 1, MODE>(g, stream);
+    if (bn == 128) return launch<128, INT8, W_KN, 1, MODE>(g, stream);
   }
-  if constexpr (MODE != kRes) {  // narrow tiles have no TMA-store path, which the residual epilogue needs
-    if constexpr (kMinBn <= 64) {
-      if (g.n > 32 || kMinBn == 64) return launch<64, INT8, W_KN, 1, MODE>(g, stream);
-    }
-    if constexpr (kMinBn <= 32) {
-      return launch<32, INT8, W_KN, 1, MODE>(g, stream);
-    }
+  if constexpr (kMinBn <= 64) {
+    if (bn == 64) return launch<64, INT8, W_KN, 1, MODE>(g, stream);
+  }
+  if constexpr (kMinBn <= 32) {
+    if (bn == 32) return launch<32, INT8, W_KN, 1, MODE>(g, stream);
   }
   return LC0B200_ERR_UNSUPPORTED;
 }
