@@ -71,7 +71,10 @@ struct TileCfg {
   static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 512 /*barriers*/;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
   static constexpr int kFit = (227 * 1024 - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+#ifndef LC0B200_GEMM_MAX_STAGES
+#define LC0B200_GEMM_MAX_STAGES 8
+#endif
+  static constexpr int kStages = kFit > LC0B200_GEMM_MAX_STAGES ? LC0B200_GEMM_MAX_STAGES : kFit;
   static_assert(kStages >= 3, "pipeline too shallow");
   static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
 };
@@ -269,6 +272,22 @@ __device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* 
   return __uint_as_float(raw);
 }
 
+// Wait-time accounting for tuning (compiled in with -DLC0B200_GEMM_PROFILE only): cycles each role
+// spends blocked, summed over CTAs.  [0] producer on a free stage, [1] MMA issuer on a free
+// accumulator, [2] MMA issuer on operands, [3] epilogue warp 0 on a complete accumulator,
+// [4] epilogue warp 0 from accumulator complete to accumulator released, [5] the same warp's
+// remaining tile time (fence + stores), [6] whole-kernel cycles of thread 0, [7] CTAs.
+#ifdef LC0B200_GEMM_PROFILE
+__device__ unsigned long long g_gemm_profile[16];
+__device__ __forceinline__ long long prof_now() { return clock64(); }
+__device__ __forceinline__ void prof_add(int slot, long long cycles) {
+  atomicAdd(&g_gemm_profile[slot], static_cast<unsigned long long>(cycles));
+}
+#else
+__device__ __forceinline__ long long prof_now() { return 0; }
+__device__ __forceinline__ void prof_add(int, long long) {}
+#endif
+
 template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS>
 __global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE, SETS>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -312,6 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int n_tiles = (p.n + BN - 1) / BN;
   const long long num_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.k + kElemsPerRow - 1) / kElemsPerRow;
+  const long long prof_start = prof_now();
 
   if (threadIdx.x == 0) {
     abort_flag_storage = 0;
@@ -348,16 +368,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (every CTA loads its own operands)
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (long long tile = group; tile < num_tiles && ok; tile += num_groups) {
-        const int m0 = static_cast<int>(tile / n_tiles) * kTileM + static_cast<int>(rank) * kBM;
-        const int n0 = static_cast<int>(tile % n_tiles) * BN + static_cast<int>(rank) * Cfg::kBRows;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
-          if (!ok) break;
+    // The whole warp follows the loop; one elected lane issues the copies.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    long long prof_wait = 0;
+    for (long long tile = group; tile < num_tiles && ok; tile += num_groups) {
+      const int m0 = static_cast<int>(tile / n_tiles) * kTileM + static_cast<int>(rank) * kBM;
+      const int n0 = static_cast<int>(tile % n_tiles) * BN + static_cast<int>(rank) * Cfg::kBRows;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const long long prof_t = prof_now();
+        ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        prof_wait += prof_now() - prof_t;
+        if (!ok) break;
+        if (ptx::elect_one()) {
           // Transaction bytes of both CTAs complete on the leader's barrier.
           const uint32_t full = (CTAS == 2) ? ptx::map_to_cta(bar_full + 8 * stage, 0u) : bar_full + 8 * stage;
           if (rank == 0) ptx::mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes * CTAS);
@@ -372,56 +397,80 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else {
             ptx::tma_load_2d<CTAS>(smem_b + stage * Cfg::kBBytes, &map_w, k0, n0, full);
           }
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
+    if (lane == 0) prof_add(0, prof_wait);
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
       constexpr uint32_t idesc = ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kTileM),
                                                  static_cast<uint32_t>(BN));
       int stage = 0;
       uint32_t phase = 0;
       uint32_t local = 0;
       bool ok = true;
+      long long prof_acc = 0, prof_ops = 0, prof_first = 0, prof_early = 0, prof_late_blocks = 0, prof_blocks = 0;
       for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
+        const long long prof_t = prof_now();
         ok = ptx::mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 0x200u + acc);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        prof_acc += prof_now() - prof_t;
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const long long prof_t2 = prof_now();
           ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 0x300u + stage);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          {
+            const long long waited = prof_now() - prof_t2;
+            prof_ops += waited;
+            if (kb == 0) prof_first += waited; else if (kb < 4) prof_early += waited;
+            prof_late_blocks += waited > 100 ? 1 : 0;
+            prof_blocks += 1;
+          }
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_a + stage * Cfg::kABytes;
           const uint32_t b_addr = smem_b + stage * Cfg::kBBytes;
+          if (ptx::elect_one()) {
 #pragma unroll
-          for (int j = 0; j < kMmaPerStage; ++j) {
-            // A: K-major, 8-row groups 1024 B apart; K advance = 32 B inside the swizzle row.
-            const uint64_t da = ptx::smem_desc_sw128(a_addr + j * 32, 16, 1024);
-            // W: K-major as A, or MN-major: 128-byte rows run along N, one row per K index,
-            //    8-row groups 1024 B apart (SBO), N panels kPanelBytes apart (LBO).
-            const uint64_t db = W_KN ? ptx::smem_desc_sw128(b_addr + j * kUmmaK * kRowBytes, kPanelBytes, 1024)
-                                     : ptx::smem_desc_sw128(b_addr + j * 32, 16, 1024);
-            const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
-            ptx::mma<INT8, CTAS>(tmem_d, da, db, idesc, accumulate);
+            for (int j = 0; j < kMmaPerStage; ++j) {
+              // A: K-major, 8-row groups 1024 B apart; K advance = 32 B inside the swizzle row.
+              const uint64_t da = ptx::smem_desc_sw128(a_addr + j * 32, 16, 1024);
+              // W: K-major as A, or MN-major: 128-byte rows run along N, one row per K index,
+              //    8-row groups 1024 B apart (SBO), N panels kPanelBytes apart (LBO).
+              const uint64_t db = W_KN ? ptx::smem_desc_sw128(b_addr + j * kUmmaK * kRowBytes, kPanelBytes, 1024)
+                                       : ptx::smem_desc_sw128(b_addr + j * 32, 16, 1024);
+              const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+              ptx::mma<INT8, CTAS>(tmem_d, da, db, idesc, accumulate);
+            }
+            // Free the smem stage (in both CTAs) once these MMAs have read it.
+            ptx::tc_commit<CTAS>(bar_empty + 8 * stage);
           }
-          // Free the smem stage (in both CTAs) once these MMAs have read it.
-          ptx::tc_commit<CTAS>(bar_empty + 8 * stage);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        ptx::tc_commit<CTAS>(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue (both CTAs)
+        if (ptx::elect_one()) ptx::tc_commit<CTAS>(bar_acc_full + 8 * acc);  // accumulator complete -> epilogue (both CTAs)
+      }
+      if (lane == 0) {
+        prof_add(1, prof_acc);
+        prof_add(2, prof_ops);
+        prof_add(8, prof_first);
+        prof_add(9, prof_early);
+        prof_add(10, prof_late_blocks);
+        prof_add(11, prof_blocks);
       }
     }
     __syncwarp();
@@ -438,6 +487,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
+    long long prof_wait = 0, prof_math = 0, prof_store = 0;
     for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
       const long long m0 = (tile / n_tiles) * kTileM + rank * kBM;
       const int n0 = static_cast<int>(tile % n_tiles) * BN + half * kColsPerWarp;
@@ -490,7 +540,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
       }
 
+      const long long prof_t = prof_now();
       ok = ptx::mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status, 0x400u + acc);
+      const long long prof_t1 = prof_now();
+      prof_wait += prof_t1 - prof_t;
       if (!ok) break;
       ptx::tc_fence_after_sync();
       if constexpr (MODE == kRes) {
@@ -510,10 +563,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int col0 = n0 + g * 64;
             if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
             uint32_t v[64];
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 4)
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(static_cast<float>(lane + j + g) * 0.01f);
+            const uint32_t buf = staging + g * kGroupBytes;
+#else
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             const uint32_t buf = staging + g * kGroupBytes;
             ptx::tc_wait_ld();
+#endif
             const bool whole = p.vec_ok && (col0 + 64 <= p.n);
             float sum = 0.0f, sumsq = 0.0f;
             // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor maps use:
@@ -532,16 +591,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
               }
               uint32_t pk[16];
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 1)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = v[h * 32 + 2 * j] ^ (v[h * 32 + 2 * j + 1] >> 16) ^ (MODE == kRes ? skip_raw[j] : 0u);
+#else
               if (whole) {
                 finish32<MODE, INT8, true>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
               } else {
                 finish32<MODE, INT8, false>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
               }
+#endif
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
+              {
+                uint32_t x = 0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) x ^= pk[j];
+                if (x == 0x12345678u && p.n < 0) ptx::st_shared_v4(row_addr, x, x, x, x);
+              }
+#else
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
                                   pk[4 * c + 2], pk[4 * c + 3]);
               }
+#endif
             }
             if (MODE == kRes) {
               // One partial per 64 output columns: part index col0 / 64, layout [part][row].
@@ -559,9 +632,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
           released = true;
+          prof_math += prof_now() - prof_t1;
           // One proxy fence per tile and warp (it is by far the most expensive instruction here),
           // then the stores of all groups.
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
+          if (n0 < p.n && p.n < 0) {
+#else
           if (n0 < p.n) {
+#endif
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -644,6 +722,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       }
+      prof_store += prof_now() - prof_t1;
+    }
+    if (ew == 0 && lane == 0) {
+      prof_add(3, prof_wait);
+      prof_add(4, prof_math);
+      prof_add(5, prof_store - prof_math);
     }
     if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
@@ -654,6 +738,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   // Neither CTA of a pair may leave while the other can still signal its barriers or read its smem.
   if (CTAS == 2) ptx::cluster_sync();
+  if (threadIdx.x == 0) {
+    prof_add(6, prof_now() - prof_start);
+    prof_add(7, 1);
+  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     if (CTAS == 2) {
@@ -665,6 +753,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------- host side
+
+#ifdef LC0B200_GEMM_PROFILE
+}  // namespace
+}  // namespace lc0b200
+// Copies the eight wait-time counters to `out8` (host memory) and zeroes them.  Synchronises the device.
+extern "C" __attribute__((visibility("default"))) int lc0b200_debug_gemm_profile(unsigned long long* out8) {  // 16 counters
+  unsigned long long zero[16] = {0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  if (cudaMemcpyFromSymbol(out8, lc0b200::g_gemm_profile, sizeof(zero)) != cudaSuccess) return 1;
+  if (cudaMemcpyToSymbol(lc0b200::g_gemm_profile, zero, sizeof(zero)) != cudaSuccess) return 1;
+  return 0;
+}
+namespace lc0b200 {
+namespace {
+#endif
 
 // LC0B200_GEMM_PAIRS=0 in the environment keeps every GEMM on the single-CTA kernel (measurement aid).
 bool pair_kernels_enabled() {

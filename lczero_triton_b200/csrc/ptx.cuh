@@ -51,6 +51,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
+// One lane of a fully converged warp (the same lane on every call).  Loops whose control flow the
+// whole warp follows, with only the asynchronous instruction itself issued by the elected lane,
+// let the compiler keep descriptors and addresses in warp-uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles of the CTA:
 // once any role gives up, every other wait in the CTA returns false too.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
