@@ -17,6 +17,7 @@ using bf16 = __nv_bfloat16;
 unsigned int* device_status_words();
 
 constexpr unsigned int kDeviceWaitTimeout = 1;
+constexpr unsigned int kDeviceSmemMisaligned = 2;  // a kernel found its shared-memory window not 1024-byte aligned
 
 __host__ __device__ inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 

@@ -68,7 +68,11 @@ struct TileCfg {
   static constexpr int kSets = kTmaStore ? SETS : 1;
   static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups * kSets;
   static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
-  static constexpr int kFixedBytes = kStagingBytes + 1024 /*align*/ + 512 /*barriers*/;
+  // Per-column epilogue vectors of the current tile, refreshed once per tile: fp32 c and d (kLnIn), or
+  // fp32 dequantisation scales plus bf16 bias, gamma and beta (other flavours).
+  static constexpr int kVecBytes = (MODE == kLnIn ? 8 : 10) * BN;
+  // The dynamic shared-memory window is declared 1024-byte aligned (the kernel checks), so no slack.
+  static constexpr int kFixedBytes = kStagingBytes + 512 /*barriers*/ + kVecBytes;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
   static constexpr int kFit = (227 * 1024 - kFixedBytes) / kStageBytes;
 #ifndef LC0B200_GEMM_MAX_STAGES
@@ -143,7 +147,12 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 template <bool VEC>
 __device__ __forceinline__ void load8_bf16(const bf16* ptr, int valid, float (&f)[8]) {
   if (VEC) {
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 8)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.5f + j;
+#else
     unpack8(__ldg(reinterpret_cast<const uint4*>(ptr)), f);
+#endif
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = j < valid ? __bfloat162float(ptr[j]) : 0.0f;
@@ -153,13 +162,77 @@ __device__ __forceinline__ void load8_bf16(const bf16* ptr, int valid, float (&f
 template <bool VEC>
 __device__ __forceinline__ void load8_f32(const float* ptr, int valid, float fill, float (&f)[8]) {
   if (VEC) {
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 8)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.25f + j;
+#else
     const float4 a = __ldg(reinterpret_cast<const float4*>(ptr));
     const float4 b = __ldg(reinterpret_cast<const float4*>(ptr) + 1);
     f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+#endif
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = j < valid ? ptr[j] : fill;
   }
+}
+
+// Per-column vectors of one output column, as one epilogue thread carries them from global memory
+// to the shared-memory vector area (a tile ahead, so the load latency is never waited for).
+struct ColRegs {
+  float f0, f1;          // kLnIn: c, d;  otherwise f0 = int8 dequantisation scale
+  uint16_t b0, b1, b2;   // bias, gamma, beta as bf16 bits
+};
+
+template <int MODE, bool INT8>
+__device__ __forceinline__ ColRegs load_cols(const KernelParams& p, int col) {
+  ColRegs r;
+  r.f0 = INT8 ? 1.0f : 0.0f;
+  r.f1 = 0.0f;
+  r.b0 = r.b1 = r.b2 = 0;
+  if (col < p.n) {
+    if (MODE == kLnIn) {
+      r.f0 = __ldg(p.ln_in_c + col);
+      r.f1 = __ldg(p.ln_in_d + col);
+    } else {
+      if (INT8 && p.col_scale != nullptr) r.f0 = __ldg(p.col_scale + col);
+      if (p.bias != nullptr) r.b0 = __ldg(reinterpret_cast<const uint16_t*>(p.bias) + col);
+      if (MODE == kRes && p.res_stats != nullptr) {
+        r.b1 = __ldg(reinterpret_cast<const uint16_t*>(p.res_gamma) + col);
+        r.b2 = __ldg(reinterpret_cast<const uint16_t*>(p.res_beta) + col);
+      }
+    }
+  }
+  return r;
+}
+
+// Layout of the vector area: kLnIn [c f32 x BN][d f32 x BN]; otherwise [scale f32 x BN][bias bf16 x BN]
+// [gamma bf16 x BN][beta bf16 x BN].  `i` is the column inside the tile.
+template <int BN, int MODE, bool INT8>
+__device__ __forceinline__ void store_cols(uint32_t vec, int i, const ColRegs& r) {
+  if (MODE == kLnIn) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * i), "r"(__float_as_uint(r.f0)) : "memory");
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * BN + 4 * i), "r"(__float_as_uint(r.f1)) : "memory");
+  } else {
+    if (INT8) asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * i), "r"(__float_as_uint(r.f0)) : "memory");
+    asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 4 * BN + 2 * i), "h"(r.b0) : "memory");
+    if (MODE == kRes) {
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 6 * BN + 2 * i), "h"(r.b1) : "memory");
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 8 * BN + 2 * i), "h"(r.b2) : "memory");
+    }
+  }
+}
+
+__device__ __forceinline__ void lds8_f32(uint32_t addr, float (&f)[8]) {
+  uint4 a, b;
+  ptx::ld_shared_v4(addr, a);
+  ptx::ld_shared_v4(addr + 16, b);
+  f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+  f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+}
+__device__ __forceinline__ void lds8_bf16(uint32_t addr, float (&f)[8]) {
+  uint4 a;
+  ptx::ld_shared_v4(addr, a);
+  unpack8(a, f);
 }
 
 // 32 output columns of one row: from raw accumulator words to packed bf16, plus the row's partial
@@ -167,9 +240,12 @@ __device__ __forceinline__ void load8_f32(const float* ptr, int valid, float fil
 // 16-byte loads of the per-column vectors (whole, aligned groups) or guarded scalar loads (matrix
 // edge, odd alignment).  The work is laid out as whole-chunk phases, each over 32 independent
 // values, so that loads are issued together and the transcendental pipe sees long independent runs.
-template <int MODE, bool INT8, bool VEC>
+// With SV the per-column vectors come from the shared-memory vector area at `vec` (tile column
+// `tcol`; columns past the matrix edge hold neutral values there, so nothing is guarded).
+template <int MODE, bool INT8, bool VEC, int BN = 0, bool SV = false>
 __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, int col0, const uint32_t* skip,
-                                         const RowCtx& r, const KernelParams& p, float& sum, float& sumsq) {
+                                         const RowCtx& r, const KernelParams& p, float& sum, float& sumsq,
+                                         uint32_t vec = 0, int tcol = 0) {
   float y[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -180,7 +256,8 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float cs[8];
-        load8_f32<VEC>(p.col_scale + col0 + g * 8, p.n - col0 - g * 8, 1.0f, cs);
+        if (SV) lds8_f32(vec + 4 * (tcol + g * 8), cs);
+        else load8_f32<VEC>(p.col_scale + col0 + g * 8, p.n - col0 - g * 8, 1.0f, cs);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[g * 8 + j] *= cs[j];
       }
@@ -190,14 +267,16 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float c[8];
-      load8_f32<VEC>(p.ln_in_c + col0 + g * 8, p.n - col0 - g * 8, 0.0f, c);
+      if (SV) lds8_f32(vec + 4 * (tcol + g * 8), c);
+      else load8_f32<VEC>(p.ln_in_c + col0 + g * 8, p.n - col0 - g * 8, 0.0f, c);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] = r.rstd * (y[g * 8 + j] - r.mean * c[j]);
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float d[8];
-      load8_f32<VEC>(p.ln_in_d + col0 + g * 8, p.n - col0 - g * 8, 0.0f, d);
+      if (SV) lds8_f32(vec + 4 * BN + 4 * (tcol + g * 8), d);
+      else load8_f32<VEC>(p.ln_in_d + col0 + g * 8, p.n - col0 - g * 8, 0.0f, d);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] += d[j];
     }
@@ -205,7 +284,8 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float b[8];
-      load8_bf16<VEC>(p.bias + col0 + g * 8, p.n - col0 - g * 8, b);
+      if (SV) lds8_bf16(vec + 4 * BN + 2 * (tcol + g * 8), b);
+      else load8_bf16<VEC>(p.bias + col0 + g * 8, p.n - col0 - g * 8, b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] += b[j];
     }
@@ -222,14 +302,16 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float ga[8];
-        load8_bf16<VEC>(p.res_gamma + col0 + g * 8, p.n - col0 - g * 8, ga);
+        if (SV) lds8_bf16(vec + 6 * BN + 2 * (tcol + g * 8), ga);
+        else load8_bf16<VEC>(p.res_gamma + col0 + g * 8, p.n - col0 - g * 8, ga);
 #pragma unroll
         for (int j = 0; j < 8; ++j) t[g * 8 + j] = (t[g * 8 + j] - r.mean) * r.rstd * ga[j];
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float be[8];
-        load8_bf16<VEC>(p.res_beta + col0 + g * 8, p.n - col0 - g * 8, be);
+        if (SV) lds8_bf16(vec + 8 * BN + 2 * (tcol + g * 8), be);
+        else load8_bf16<VEC>(p.res_beta + col0 + g * 8, p.n - col0 - g * 8, be);
 #pragma unroll
         for (int j = 0; j < 8; ++j) t[g * 8 + j] += be[j];
       }
@@ -240,7 +322,11 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
   // The activation code is uniform for the launch: branch once per chunk, not per element.
   if (p.activation == LC0B200_ACT_MISH) {
 #pragma unroll
+#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 16)
+    for (int j = 0; j < 32; ++j) y[j] = y[j] * 1.5f;
+#else
     for (int j = 0; j < 32; ++j) y[j] = act_mish(y[j]);
+#endif
   } else if (p.activation == LC0B200_ACT_RELU) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.0f);
@@ -252,7 +338,7 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
   for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
   if (MODE == kRes) {
     if (p.stats_out != nullptr) {
-      const int valid = VEC ? 32 : p.n - col0;
+      const int valid = (VEC || SV) ? 32 : p.n - col0;  // (SV: columns past the edge come out as exact zeros)
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 f = unpack_bf16x2(packed[j]);  // what the consumer will read
@@ -305,8 +391,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   static_assert(!W_KN || (Cfg::kBRows % kPanelN == 0), "MN-major weight staging needs whole 128-byte panels");
   static_assert(MODE != kRes || Cfg::kTmaStore, "the residual epilogue needs the TMA-store layout");
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = ptx::smem_u32(smem_raw);  // 1024-byte aligned (checked below): the swizzle needs it
   const uint32_t smem_a = smem_base;
   const uint32_t smem_b = smem_base + kStages * Cfg::kABytes;
   const uint32_t staging_base = smem_base + kStages * Cfg::kStageBytes;  // 1024-byte aligned
@@ -316,9 +402,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t bar_acc_full = bar_base + 16 * kStages;       // [2]
   const uint32_t bar_acc_empty = bar_base + 16 * kStages + 16; // [2]  (used in the leader CTA only)
   const uint32_t bar_skip = bar_base + 16 * kStages + 32;      // [kEpilogueWarps] skip tile landed (kRes)
-  const uint32_t tmem_slot = bar_skip + 8 * Cfg::kEpilogueWarps;
-  __shared__ int abort_flag_storage;
-  volatile int* abort_flag = &abort_flag_storage;
+  const uint32_t bar_vec_ready = bar_skip + 8 * Cfg::kEpilogueWarps;  // this tile's column vectors are in place
+  const uint32_t bar_vec_free = bar_vec_ready + 8;                    // ... and have been read by every warp
+  const uint32_t tmem_slot = bar_vec_free + 8;
+  const uint32_t vec_base = bar_base + 512;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 4 - smem_base));
+  static_assert(16 * 8 + 32 + 8 * 8 + 16 + 8 <= 512, "barrier area too small");
+  if ((smem_base & 1023u) != 0u) {  // never seen; refuse loudly rather than mis-swizzle
+    if (threadIdx.x == 0 && atomicCAS(&p.status[0], 0u, kDeviceSmemMisaligned) == 0u) p.status[1] = smem_base;
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -334,7 +427,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const long long prof_start = prof_now();
 
   if (threadIdx.x == 0) {
-    abort_flag_storage = 0;
+    *abort_flag = 0;
+    ptx::mbar_init(bar_vec_ready, Cfg::kEpilogueWarps);
+    ptx::mbar_init(bar_vec_free, Cfg::kEpilogueWarps);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
@@ -487,7 +582,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
-    long long prof_wait = 0, prof_math = 0, prof_store = 0;
+    long long prof_wait = 0, prof_math = 0, prof_store = 0, prof_ld = 0, prof_alu = 0;
+    // Column of the tile this thread carries to the vector area (threads past BN carry none).
+    const int vec_col = static_cast<int>(threadIdx.x) - 64;
+    ColRegs cols = {};
+    if (tma_path && vec_col < BN && group < num_tiles) {
+      cols = load_cols<MODE, INT8>(p, static_cast<int>(group % n_tiles) * BN + vec_col);
+    }
     for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
       const long long m0 = (tile / n_tiles) * kTileM + rank * kBM;
       const int n0 = static_cast<int>(tile % n_tiles) * BN + half * kColsPerWarp;
@@ -496,6 +597,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.m;
       const uint32_t staging = staging_warp + (Cfg::kSets == 2 ? (local & 1u) : 0u) * Cfg::kGroups * kGroupBytes;
+
+      if (tma_path) {
+        // Column vectors: wait until every warp is done with the previous tile's, put this tile's in
+        // place, then start the next tile's on their way.
+        if (local > 0) {
+          ok = ptx::mbar_wait(bar_vec_free, (local - 1u) & 1u, abort_flag, p.status, 0x600u);
+          if (!ok) break;
+        }
+        if (vec_col < BN) store_cols<BN, MODE, INT8>(vec_base, vec_col, cols);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_vec_ready);
+        const long long next = tile + num_groups;
+        if (vec_col < BN && next < num_tiles) {
+          cols = load_cols<MODE, INT8>(p, static_cast<int>(next % n_tiles) * BN + vec_col);
+        }
+      }
 
       // ---- everything that can be fetched before the accumulator is complete
       RowCtx rc;
@@ -553,6 +670,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           skip_phase ^= 1u;
         }
       }
+      if (tma_path) {
+        ok = ptx::mbar_wait(bar_vec_ready, local & 1u, abort_flag, p.status, 0x700u);
+        if (!ok) break;
+      }
       const uint32_t taddr_row =
           tmem_base + acc * BN + half * kColsPerWarp + (static_cast<uint32_t>(quarter * 32) << 16);
       bool released = false;  // accumulator already handed back to the MMA issuer
@@ -563,6 +684,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int col0 = n0 + g * 64;
             if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
             uint32_t v[64];
+            const long long prof_g0 = prof_now();
 #if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 4)
 #pragma unroll
             for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(static_cast<float>(lane + j + g) * 0.01f);
@@ -573,7 +695,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t buf = staging + g * kGroupBytes;
             ptx::tc_wait_ld();
 #endif
-            const bool whole = p.vec_ok && (col0 + 64 <= p.n);
+            const long long prof_g1 = prof_now();
+            prof_ld += prof_g1 - prof_g0;
             float sum = 0.0f, sumsq = 0.0f;
             // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor maps use:
             // 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
@@ -595,11 +718,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
               for (int j = 0; j < 16; ++j) pk[j] = v[h * 32 + 2 * j] ^ (v[h * 32 + 2 * j + 1] >> 16) ^ (MODE == kRes ? skip_raw[j] : 0u);
 #else
-              if (whole) {
-                finish32<MODE, INT8, true>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
-              } else {
-                finish32<MODE, INT8, false>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq);
-              }
+              finish32<MODE, INT8, true, BN, true>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq, vec_base,
+                                                   half * kColsPerWarp + g * 64 + h * 32);
 #endif
 #if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
               {
@@ -616,6 +736,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               }
 #endif
             }
+            prof_alu += prof_now() - prof_g1;
             if (MODE == kRes) {
               // One partial per 64 output columns: part index col0 / 64, layout [part][row].
               if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
@@ -630,6 +751,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             } else {
               ptx::mbar_arrive(bar_acc_empty + 8 * acc);
             }
+            ptx::mbar_arrive(bar_vec_free);
           }
           released = true;
           prof_math += prof_now() - prof_t1;
@@ -728,6 +850,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       prof_add(3, prof_wait);
       prof_add(4, prof_math);
       prof_add(5, prof_store - prof_math);
+      prof_add(12, prof_ld);
+      prof_add(13, prof_alu);
     }
     if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
