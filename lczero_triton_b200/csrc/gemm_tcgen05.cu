@@ -68,9 +68,9 @@ struct TileCfg {
   static constexpr int kSets = kTmaStore ? SETS : 1;
   static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups * kSets;
   static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
-  // Per-column epilogue vectors of the current tile, refreshed once per tile: fp32 c and d (kLnIn), or
-  // fp32 dequantisation scales plus bf16 bias, gamma and beta (other flavours).
-  static constexpr int kVecBytes = (MODE == kLnIn ? 8 : 10) * BN;
+  // Per-column epilogue vectors of the current tile, refreshed once per tile (two fp32 vectors and,
+  // for the residual flavour, one bf16 vector: see ColRegs).
+  static constexpr int kVecBytes = (MODE == kRes ? 10 : 8) * BN;
   // The dynamic shared-memory window is declared 1024-byte aligned (the kernel checks), so no slack.
   static constexpr int kFixedBytes = kStagingBytes + 512 /*barriers*/ + kVecBytes;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
@@ -120,6 +120,7 @@ struct RowCtx {
   float rs;       // int8: activation scale of this row
   float mean;     // kLnIn: mean and 1/sqrt(var + eps) of this row of A;  kRes: of this row of the skip operand
   float rstd;
+  float nmean;    // kLnIn: -mean;  kRes: -mean * rstd  (the fused multiply-add forms of finish32_sv)
   bool row_ok;
 };
 
@@ -178,9 +179,15 @@ __device__ __forceinline__ void load8_f32(const float* ptr, int valid, float fil
 
 // Per-column vectors of one output column, as one epilogue thread carries them from global memory
 // to the shared-memory vector area (a tile ahead, so the load latency is never waited for).
+// They are pre-combined so that the per-element arithmetic is a short chain of fused multiply-adds:
+//   kLnIn : f0 = c, f1 = d                       y = rstd * (acc - mean * c) + d
+//   kPlain: f0 = int8 scale, f1 = bias           y = acc * f0 + f1
+//   kRes  : f0 = int8 scale, f1 = beta + alpha * bias, g = gamma
+//                                               y = alpha * acc * f0 + ((skip - mean) * rstd * g + f1)
+// Columns past the matrix edge carry zeros (scale 1), so they produce exact zeros and need no guard.
 struct ColRegs {
-  float f0, f1;          // kLnIn: c, d;  otherwise f0 = int8 dequantisation scale
-  uint16_t b0, b1, b2;   // bias, gamma, beta as bf16 bits
+  float f0, f1;
+  uint16_t g;  // bf16 bits
 };
 
 template <int MODE, bool INT8>
@@ -188,38 +195,37 @@ __device__ __forceinline__ ColRegs load_cols(const KernelParams& p, int col) {
   ColRegs r;
   r.f0 = INT8 ? 1.0f : 0.0f;
   r.f1 = 0.0f;
-  r.b0 = r.b1 = r.b2 = 0;
+  r.g = 0;
   if (col < p.n) {
     if (MODE == kLnIn) {
       r.f0 = __ldg(p.ln_in_c + col);
       r.f1 = __ldg(p.ln_in_d + col);
     } else {
       if (INT8 && p.col_scale != nullptr) r.f0 = __ldg(p.col_scale + col);
-      if (p.bias != nullptr) r.b0 = __ldg(reinterpret_cast<const uint16_t*>(p.bias) + col);
-      if (MODE == kRes && p.res_stats != nullptr) {
-        r.b1 = __ldg(reinterpret_cast<const uint16_t*>(p.res_gamma) + col);
-        r.b2 = __ldg(reinterpret_cast<const uint16_t*>(p.res_beta) + col);
+      const float b = p.bias != nullptr ? __bfloat162float(p.bias[col]) : 0.0f;
+      if (MODE == kRes) {
+        r.f1 = p.res_alpha * b;
+        r.g = 0x3F80u;  // 1.0: a skip operand that is added as it is
+        if (p.res_stats != nullptr) {
+          r.f1 += __bfloat162float(p.res_beta[col]);
+          r.g = __ldg(reinterpret_cast<const uint16_t*>(p.res_gamma) + col);
+        }
+      } else {
+        r.f1 = b;
       }
     }
   }
   return r;
 }
 
-// Layout of the vector area: kLnIn [c f32 x BN][d f32 x BN]; otherwise [scale f32 x BN][bias bf16 x BN]
-// [gamma bf16 x BN][beta bf16 x BN].  `i` is the column inside the tile.
+// Layout of the vector area: [f0 f32 x BN][f1 f32 x BN][g bf16 x BN (kRes)].  `i` is the column inside the tile.
 template <int BN, int MODE, bool INT8>
 __device__ __forceinline__ void store_cols(uint32_t vec, int i, const ColRegs& r) {
-  if (MODE == kLnIn) {
+  if (MODE == kLnIn || INT8) {
     asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * i), "r"(__float_as_uint(r.f0)) : "memory");
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * BN + 4 * i), "r"(__float_as_uint(r.f1)) : "memory");
-  } else {
-    if (INT8) asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * i), "r"(__float_as_uint(r.f0)) : "memory");
-    asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 4 * BN + 2 * i), "h"(r.b0) : "memory");
-    if (MODE == kRes) {
-      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 6 * BN + 2 * i), "h"(r.b1) : "memory");
-      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 8 * BN + 2 * i), "h"(r.b2) : "memory");
-    }
   }
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(vec + 4 * BN + 4 * i), "r"(__float_as_uint(r.f1)) : "memory");
+  if (MODE == kRes) asm volatile("st.shared.b16 [%0], %1;" ::"r"(vec + 8 * BN + 2 * i), "h"(r.g) : "memory");
 }
 
 __device__ __forceinline__ void lds8_f32(uint32_t addr, float (&f)[8]) {
@@ -235,17 +241,127 @@ __device__ __forceinline__ void lds8_bf16(uint32_t addr, float (&f)[8]) {
   unpack8(a, f);
 }
 
+// 2^t for t in [-126, 127]: nearest-integer split by the 1.5 * 2^23 trick, a cubic on the fraction in
+// [-0.5, 0.5] (relative error 7.5e-5, far below bf16 resolution), the integer part added to the exponent
+// field.  Runs on the FMA and integer pipes, leaving the transcendental unit to other elements.
+__device__ __forceinline__ float exp2_fma(float t) {
+  const float tf = t + 12582912.0f;
+  const float f = t - (tf - 12582912.0f);
+  float q = fmaf(0.05517167f, f, 0.24261113f);
+  q = fmaf(q, f, 0.69326097f);
+  q = fmaf(q, f, 0.99992806f);
+  return __int_as_float(__float_as_int(q) + (__float_as_int(tf) << 23));
+}
+
+#ifndef LC0B200_MISH_POLY
+#define LC0B200_MISH_POLY 0  // 0: every exp on the transcendental unit, 1: every second one, 2: none
+#endif
+
+// mish(x) = x * n / (n + 2) with n = e^x (e^x + 2) (reference formula: bt4/kernels/layer_norm.py:61-69,
+// which switches between n*q and x - 2q by range; with x clamped to <= 20 in the exponential the single
+// form is accurate everywhere: n / (n + 2) rounds to 1 from x = 9 on and tends to n / 2 for x -> -inf).
+// 32 values at a time: one reciprocal serves two elements (1/da = db / (da db)), and the exponentials
+// alternate between the transcendental unit and exp2_fma, so both pipes stay busy.
+__device__ __forceinline__ void mish32(float (&y)[32]) {
+  constexpr float kLog2e = 1.4426950408889634f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float a = y[2 * j], b = y[2 * j + 1];
+    float ea, eb;
+    if (LC0B200_MISH_POLY == 2) {
+      ea = exp2_fma(fmaxf(fminf(a, 20.0f), -80.0f) * kLog2e);
+    } else {
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ea) : "f"(fminf(a, 20.0f) * kLog2e));
+    }
+    if (LC0B200_MISH_POLY >= 1) {
+      eb = exp2_fma(fmaxf(fminf(b, 20.0f), -80.0f) * kLog2e);
+    } else {
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eb) : "f"(fminf(b, 20.0f) * kLog2e));
+    }
+    const float na = ea * (ea + 2.0f), nb = eb * (eb + 2.0f);
+    const float da = na + 2.0f, db = nb + 2.0f;  // in [2, 2.4e17]: the product stays finite
+#if defined(LC0B200_MISH_PAIR) && LC0B200_MISH_PAIR == 0
+    float ra, rb;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(da));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rb) : "f"(db));
+    y[2 * j] = a * (na * ra);
+    y[2 * j + 1] = b * (nb * rb);
+#else
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(da * db));
+    y[2 * j] = a * (na * (db * r));
+    y[2 * j + 1] = b * (nb * (da * r));
+#endif
+  }
+}
+
+// The TMA-store epilogue's form of finish32 (below): per-column vectors come pre-combined from the
+// shared-memory vector area at `vec` (tile column `tcol`), see ColRegs.
+template <int MODE, bool INT8, int BN>
+__device__ __forceinline__ void finish32_sv(const uint32_t* v, uint32_t* packed, const uint32_t* skip, const RowCtx& r,
+                                            const KernelParams& p, float& sum, float& sumsq, uint32_t vec, int tcol) {
+  float y[32];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float f0[8], f1[8];
+    if (MODE == kLnIn || INT8) lds8_f32(vec + 4 * (tcol + g * 8), f0);
+    lds8_f32(vec + 4 * BN + 4 * (tcol + g * 8), f1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = g * 8 + j;
+      float a = INT8 ? static_cast<float>(static_cast<int>(v[e])) * r.rs : __uint_as_float(v[e]);
+      if (MODE == kLnIn) {
+        y[e] = fmaf(r.rstd, fmaf(r.nmean, f0[j], a), f1[j]);
+      } else {
+        if (INT8) a *= f0[j];
+        if (MODE == kPlain) y[e] = a + f1[j];
+        else y[e] = a;  // finished below, once the skip values are unpacked
+      }
+    }
+    if (MODE == kRes) {
+      float ga[8];
+      lds8_bf16(vec + 8 * BN + 2 * (tcol + g * 8), ga);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack_bf16x2(skip[g * 4 + j]);
+        const int e = g * 8 + 2 * j;
+        y[e] = fmaf(p.res_alpha, y[e], fmaf(fmaf(t.x, r.rstd, r.nmean), ga[2 * j], f1[2 * j]));
+        y[e + 1] = fmaf(p.res_alpha, y[e + 1], fmaf(fmaf(t.y, r.rstd, r.nmean), ga[2 * j + 1], f1[2 * j + 1]));
+      }
+    }
+  }
+  // The activation code is uniform for the launch: branch once per chunk, not per element.
+  if (p.activation == LC0B200_ACT_MISH) {
+    mish32(y);
+  } else if (p.activation == LC0B200_ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.0f);
+  } else if (p.activation == LC0B200_ACT_SWISH) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = act_swish(y[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
+  if (MODE == kRes) {
+    if (p.stats_out != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 f = unpack_bf16x2(packed[j]);  // what the consumer will read
+        sum += f.x + f.y;
+        sumsq = fmaf(f.x, f.x, fmaf(f.y, f.y, sumsq));
+      }
+    }
+  }
+}
+
 // 32 output columns of one row: from raw accumulator words to packed bf16, plus the row's partial
 // sums of what is stored.  `skip` holds the 32 skip values as packed bf16 pairs (kRes).  VEC selects
 // 16-byte loads of the per-column vectors (whole, aligned groups) or guarded scalar loads (matrix
 // edge, odd alignment).  The work is laid out as whole-chunk phases, each over 32 independent
 // values, so that loads are issued together and the transcendental pipe sees long independent runs.
-// With SV the per-column vectors come from the shared-memory vector area at `vec` (tile column
-// `tcol`; columns past the matrix edge hold neutral values there, so nothing is guarded).
-template <int MODE, bool INT8, bool VEC, int BN = 0, bool SV = false>
+template <int MODE, bool INT8, bool VEC>
 __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, int col0, const uint32_t* skip,
-                                         const RowCtx& r, const KernelParams& p, float& sum, float& sumsq,
-                                         uint32_t vec = 0, int tcol = 0) {
+                                         const RowCtx& r, const KernelParams& p, float& sum, float& sumsq) {
   float y[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -256,8 +372,7 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float cs[8];
-        if (SV) lds8_f32(vec + 4 * (tcol + g * 8), cs);
-        else load8_f32<VEC>(p.col_scale + col0 + g * 8, p.n - col0 - g * 8, 1.0f, cs);
+        load8_f32<VEC>(p.col_scale + col0 + g * 8, p.n - col0 - g * 8, 1.0f, cs);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[g * 8 + j] *= cs[j];
       }
@@ -267,16 +382,14 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float c[8];
-      if (SV) lds8_f32(vec + 4 * (tcol + g * 8), c);
-      else load8_f32<VEC>(p.ln_in_c + col0 + g * 8, p.n - col0 - g * 8, 0.0f, c);
+      load8_f32<VEC>(p.ln_in_c + col0 + g * 8, p.n - col0 - g * 8, 0.0f, c);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] = r.rstd * (y[g * 8 + j] - r.mean * c[j]);
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float d[8];
-      if (SV) lds8_f32(vec + 4 * BN + 4 * (tcol + g * 8), d);
-      else load8_f32<VEC>(p.ln_in_d + col0 + g * 8, p.n - col0 - g * 8, 0.0f, d);
+      load8_f32<VEC>(p.ln_in_d + col0 + g * 8, p.n - col0 - g * 8, 0.0f, d);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] += d[j];
     }
@@ -284,8 +397,7 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       float b[8];
-      if (SV) lds8_bf16(vec + 4 * BN + 2 * (tcol + g * 8), b);
-      else load8_bf16<VEC>(p.bias + col0 + g * 8, p.n - col0 - g * 8, b);
+      load8_bf16<VEC>(p.bias + col0 + g * 8, p.n - col0 - g * 8, b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[g * 8 + j] += b[j];
     }
@@ -302,16 +414,14 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float ga[8];
-        if (SV) lds8_bf16(vec + 6 * BN + 2 * (tcol + g * 8), ga);
-        else load8_bf16<VEC>(p.res_gamma + col0 + g * 8, p.n - col0 - g * 8, ga);
+        load8_bf16<VEC>(p.res_gamma + col0 + g * 8, p.n - col0 - g * 8, ga);
 #pragma unroll
         for (int j = 0; j < 8; ++j) t[g * 8 + j] = (t[g * 8 + j] - r.mean) * r.rstd * ga[j];
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float be[8];
-        if (SV) lds8_bf16(vec + 8 * BN + 2 * (tcol + g * 8), be);
-        else load8_bf16<VEC>(p.res_beta + col0 + g * 8, p.n - col0 - g * 8, be);
+        load8_bf16<VEC>(p.res_beta + col0 + g * 8, p.n - col0 - g * 8, be);
 #pragma unroll
         for (int j = 0; j < 8; ++j) t[g * 8 + j] += be[j];
       }
@@ -321,12 +431,7 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
   }
   // The activation code is uniform for the launch: branch once per chunk, not per element.
   if (p.activation == LC0B200_ACT_MISH) {
-#pragma unroll
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 16)
-    for (int j = 0; j < 32; ++j) y[j] = y[j] * 1.5f;
-#else
-    for (int j = 0; j < 32; ++j) y[j] = act_mish(y[j]);
-#endif
+    mish32(y);
   } else if (p.activation == LC0B200_ACT_RELU) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.0f);
@@ -338,7 +443,7 @@ __device__ __forceinline__ void finish32(const uint32_t* v, uint32_t* packed, in
   for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
   if (MODE == kRes) {
     if (p.stats_out != nullptr) {
-      const int valid = (VEC || SV) ? 32 : p.n - col0;  // (SV: columns past the edge come out as exact zeros)
+      const int valid = VEC ? 32 : p.n - col0;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 f = unpack_bf16x2(packed[j]);  // what the consumer will read
@@ -629,6 +734,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      rc.nmean = (MODE == kRes) ? -rc.mean * rc.rstd : -rc.mean;
       if (tma_path) {
         // The staging buffers are free once the previous tile's stores have finished reading them;
         // those were issued a whole main loop ago, so this wait is normally already satisfied.
@@ -718,8 +824,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
               for (int j = 0; j < 16; ++j) pk[j] = v[h * 32 + 2 * j] ^ (v[h * 32 + 2 * j + 1] >> 16) ^ (MODE == kRes ? skip_raw[j] : 0u);
 #else
-              finish32<MODE, INT8, true, BN, true>(&v[h * 32], pk, col0 + h * 32, skip_raw, rc, p, sum, sumsq, vec_base,
-                                                   half * kColsPerWarp + g * 64 + h * 32);
+              finish32_sv<MODE, INT8, BN>(&v[h * 32], pk, skip_raw, rc, p, sum, sumsq, vec_base,
+                                          half * kColsPerWarp + g * 64 + h * 32);
 #endif
 #if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
               {
