@@ -17,8 +17,9 @@
 // main loop of tile i+1.  The epilogue is organised so that nothing it needs from global memory is
 // on the critical path after the accumulator arrives: per-row LayerNorm statistics are read while
 // the tile is still being multiplied, the residual operand of a 32 x 64 group is brought into the
-// warp's swizzled staging buffer by TMA ahead of time, the result overwrites it in place and leaves
-// through a TMA store (full 128-byte lines, clipped at the matrix edge by the tensor map).
+// warp's swizzled staging buffer by TMA ahead of time, the result overwrites it in place and the warp
+// copies the buffer out in full 128-byte lines (a TMA store of the buffer when the row length does
+// not allow 16-byte pieces: TMA stores were measured to hold up the operand loads of the main loop).
 // f32 / raw s32 results, narrow tiles and unaligned outputs use direct stores.  Operands are staged
 // K-major with the 128-byte swizzle; the weight operand may instead be staged MN-major straight from
 // the reference's [K,N] layout.
@@ -46,10 +47,7 @@ constexpr int kGroupBytes = 32 * kRowBytes;  // staging for 32 rows x 64 bf16 co
 //   kRes  : y = alpha * (dequant(acc) + bias) + skip, skip plain or a deferred LayerNorm; row sums out
 enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 
-// SETS = 2 keeps two sets of staging buffers and alternates them tile by tile, so that a tile's
-// stores never have to be waited for by the next tile.  Used for short-K problems, where the
-// epilogue, not the main loop, sets the pace and few pipeline stages are needed.
-template <int BN, int CTAS, int MODE, int SETS = 1>
+template <int BN, int CTAS, int MODE>
 struct TileCfg {
   static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
   static constexpr int kABytes = kBM * kRowBytes;
@@ -62,11 +60,10 @@ struct TileCfg {
   static constexpr bool kTmaStore = BN >= 128;      // each epilogue warp then owns whole 64-column groups
   static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
   static constexpr int kGroups = kColsPerWarp / 64; // 64-column groups per warp and tile (TMA-store path)
-  // One staging buffer per warp and 64-column group: the residual flavour prefetches the skip
-  // operand of the whole tile into them, and every flavour can fill one buffer while the TMA store
-  // of the other is still reading it.
-  static constexpr int kSets = kTmaStore ? SETS : 1;
-  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups * kSets;
+  // One staging buffer of 32 rows x 64 columns per epilogue warp and group: the residual flavour
+  // lands the skip operand of the whole tile in them ahead of time, and every flavour parks the
+  // whole tile's results there so that copying them out happens after the accumulator is released.
+  static constexpr int kBuffersPerWarp = !kTmaStore ? 0 : kGroups;
   static constexpr int kStagingBytes = kEpilogueWarps * kBuffersPerWarp * kGroupBytes;
   // Per-column epilogue vectors of the current tile, refreshed once per tile (two fp32 vectors and,
   // for the residual flavour, one bf16 vector: see ColRegs).
@@ -96,6 +93,7 @@ struct KernelParams {
   int activation;
   int vec_ok;     // out / bias / scales / fold vectors are 16-byte aligned and ldc keeps rows aligned
   int tma_store;  // bf16 output that a tensor map can address (map_out is valid)
+  int coalesced;  // ... whose rows also split into whole 16-byte pieces: the warps copy the staging buffers out
   unsigned int* status;
   // Deferred LayerNorm (see lc0b200_gemm_args).
   const float2* ln_in_stats;
@@ -148,12 +146,7 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 template <bool VEC>
 __device__ __forceinline__ void load8_bf16(const bf16* ptr, int valid, float (&f)[8]) {
   if (VEC) {
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 8)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = 0.5f + j;
-#else
     unpack8(__ldg(reinterpret_cast<const uint4*>(ptr)), f);
-#endif
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = j < valid ? __bfloat162float(ptr[j]) : 0.0f;
@@ -163,14 +156,9 @@ __device__ __forceinline__ void load8_bf16(const bf16* ptr, int valid, float (&f
 template <bool VEC>
 __device__ __forceinline__ void load8_f32(const float* ptr, int valid, float fill, float (&f)[8]) {
   if (VEC) {
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 8)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = 0.25f + j;
-#else
     const float4 a = __ldg(reinterpret_cast<const float4*>(ptr));
     const float4 b = __ldg(reinterpret_cast<const float4*>(ptr) + 1);
     f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-#endif
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = j < valid ? ptr[j] : fill;
@@ -241,57 +229,26 @@ __device__ __forceinline__ void lds8_bf16(uint32_t addr, float (&f)[8]) {
   unpack8(a, f);
 }
 
-// 2^t for t in [-126, 127]: nearest-integer split by the 1.5 * 2^23 trick, a cubic on the fraction in
-// [-0.5, 0.5] (relative error 7.5e-5, far below bf16 resolution), the integer part added to the exponent
-// field.  Runs on the FMA and integer pipes, leaving the transcendental unit to other elements.
-__device__ __forceinline__ float exp2_fma(float t) {
-  const float tf = t + 12582912.0f;
-  const float f = t - (tf - 12582912.0f);
-  float q = fmaf(0.05517167f, f, 0.24261113f);
-  q = fmaf(q, f, 0.69326097f);
-  q = fmaf(q, f, 0.99992806f);
-  return __int_as_float(__float_as_int(q) + (__float_as_int(tf) << 23));
-}
-
-#ifndef LC0B200_MISH_POLY
-#define LC0B200_MISH_POLY 0  // 0: every exp on the transcendental unit, 1: every second one, 2: none
-#endif
-
 // mish(x) = x * n / (n + 2) with n = e^x (e^x + 2) (reference formula: bt4/kernels/layer_norm.py:61-69,
 // which switches between n*q and x - 2q by range; with x clamped to <= 20 in the exponential the single
 // form is accurate everywhere: n / (n + 2) rounds to 1 from x = 9 on and tends to n / 2 for x -> -inf).
-// 32 values at a time: one reciprocal serves two elements (1/da = db / (da db)), and the exponentials
-// alternate between the transcendental unit and exp2_fma, so both pipes stay busy.
+// 32 values at a time; one reciprocal serves two elements (1/da = db / (da db)).  (Moving exponentials
+// to a polynomial on the FMA pipe was measured slower: every extra instruction issued by the epilogue
+// warps costs more than the transcendental unit saves.)
 __device__ __forceinline__ void mish32(float (&y)[32]) {
   constexpr float kLog2e = 1.4426950408889634f;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     const float a = y[2 * j], b = y[2 * j + 1];
     float ea, eb;
-    if (LC0B200_MISH_POLY == 2) {
-      ea = exp2_fma(fmaxf(fminf(a, 20.0f), -80.0f) * kLog2e);
-    } else {
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ea) : "f"(fminf(a, 20.0f) * kLog2e));
-    }
-    if (LC0B200_MISH_POLY >= 1) {
-      eb = exp2_fma(fmaxf(fminf(b, 20.0f), -80.0f) * kLog2e);
-    } else {
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eb) : "f"(fminf(b, 20.0f) * kLog2e));
-    }
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ea) : "f"(fminf(a, 20.0f) * kLog2e));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eb) : "f"(fminf(b, 20.0f) * kLog2e));
     const float na = ea * (ea + 2.0f), nb = eb * (eb + 2.0f);
     const float da = na + 2.0f, db = nb + 2.0f;  // in [2, 2.4e17]: the product stays finite
-#if defined(LC0B200_MISH_PAIR) && LC0B200_MISH_PAIR == 0
-    float ra, rb;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(da));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rb) : "f"(db));
-    y[2 * j] = a * (na * ra);
-    y[2 * j + 1] = b * (nb * rb);
-#else
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(da * db));
     y[2 * j] = a * (na * (db * r));
     y[2 * j + 1] = b * (nb * (da * r));
-#endif
   }
 }
 
@@ -479,12 +436,12 @@ __device__ __forceinline__ long long prof_now() { return 0; }
 __device__ __forceinline__ void prof_add(int, long long) {}
 #endif
 
-template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS>
-__global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE, SETS>::kThreads, 1)
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
+__global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_skip,
                     const KernelParams p) {
-  using Cfg = TileCfg<BN, CTAS, MODE, SETS>;
+  using Cfg = TileCfg<BN, CTAS, MODE>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
   constexpr int kUmmaK = INT8 ? 32 : 16;          // K per tcgen05.mma (32 bytes)
@@ -683,7 +640,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t staging_warp = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
     const uint32_t skip_bar = bar_skip + 8 * ew;
-    const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;
+    const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;  // grouped epilogue
+    const bool coalesced = p.coalesced != 0;  // ... copied out by the warp itself (else by TMA store)
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
@@ -701,7 +659,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t acc_phase = (local >> 1) & 1u;
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.m;
-      const uint32_t staging = staging_warp + (Cfg::kSets == 2 ? (local & 1u) : 0u) * Cfg::kGroups * kGroupBytes;
+      const uint32_t staging = staging_warp;
 
       if (tma_path) {
         // Column vectors: wait until every warp is done with the previous tile's, put this tile's in
@@ -735,16 +693,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       rc.nmean = (MODE == kRes) ? -rc.mean * rc.rstd : -rc.mean;
-      if (tma_path) {
-        // The staging buffers are free once the previous tile's stores have finished reading them;
-        // those were issued a whole main loop ago, so this wait is normally already satisfied.
-        // (With two sets the buffers were last used two tiles ago: one younger group may be in flight.)
-        if (lane == 0) ptx::bulk_wait_read<Cfg::kSets - 1>();
+      if (tma_path && !coalesced) {
+        // TMA-store flavour: the staging buffers are free once the previous tile's stores have
+        // finished reading them.
+        if (lane == 0) ptx::bulk_wait_read<0>();
         __syncwarp();
       }
       if constexpr (MODE == kRes) {
         // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
         // buffers, one 32 x 64 box per group.
+        if (coalesced) {
+          // The buffers were last written and read by ordinary shared-memory accesses of this warp.
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+        }
         if (lane == 0) {
           int boxes = 0;
 #pragma unroll
@@ -791,21 +753,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
             uint32_t v[64];
             const long long prof_g0 = prof_now();
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 4)
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(static_cast<float>(lane + j + g) * 0.01f);
-            const uint32_t buf = staging + g * kGroupBytes;
-#else
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            const uint32_t buf = staging + g * kGroupBytes;
             ptx::tc_wait_ld();
-#endif
             const long long prof_g1 = prof_now();
             prof_ld += prof_g1 - prof_g0;
             float sum = 0.0f, sumsq = 0.0f;
-            // Row `lane` of a 32 x 128-byte tile in the 128-byte swizzle the tensor maps use:
-            // 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+            // Row `lane` of this group's 32 x 128-byte staging buffer (skip operand in, results out)
+            // in the 128-byte swizzle the tensor maps use: 16-byte chunk c of row r lives at
+            // chunk (c ^ (r & 7)).
+            const uint32_t buf = staging + g * kGroupBytes;
             const uint32_t row_addr = buf + lane * kRowBytes;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {  // two 32-column halves of the group
@@ -820,27 +777,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
               }
               uint32_t pk[16];
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 1)
-#pragma unroll
-              for (int j = 0; j < 16; ++j) pk[j] = v[h * 32 + 2 * j] ^ (v[h * 32 + 2 * j + 1] >> 16) ^ (MODE == kRes ? skip_raw[j] : 0u);
-#else
               finish32_sv<MODE, INT8, BN>(&v[h * 32], pk, skip_raw, rc, p, sum, sumsq, vec_base,
                                           half * kColsPerWarp + g * 64 + h * 32);
-#endif
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
-              {
-                uint32_t x = 0;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) x ^= pk[j];
-                if (x == 0x12345678u && p.n < 0) ptx::st_shared_v4(row_addr, x, x, x, x);
-              }
-#else
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
                                   pk[4 * c + 2], pk[4 * c + 3]);
               }
-#endif
+            }
+            if (!coalesced) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                ptx::tma_store_2d(&map_out, buf, col0, static_cast<int>(m0) + quarter * 32);
+                ptx::bulk_commit();
+              }
             }
             prof_alu += prof_now() - prof_g1;
             if (MODE == kRes) {
@@ -848,7 +799,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
             }
           }
-          // TMEM has been read out: hand the accumulator back before the stores are even issued.
+          // TMEM has been read out: hand the accumulator back.
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
@@ -861,25 +812,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
           released = true;
           prof_math += prof_now() - prof_t1;
-          // One proxy fence per tile and warp (it is by far the most expensive instruction here),
-          // then the stores of all groups.
-#if defined(LC0B200_GEMM_EXPERIMENT) && (LC0B200_GEMM_EXPERIMENT & 2)
-          if (n0 < p.n && p.n < 0) {
-#else
-          if (n0 < p.n) {
-#endif
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
+          if (coalesced) {
+            // Copy the tile out of the staging buffers, now that the accumulator is back with the MMA
+            // issuer: 8 lanes per row (eight 16-byte chunks = one 128-byte line), 4 rows per
+            // instruction.  n is a multiple of 8 here, so a chunk is wholly inside or outside.  The
+            // SM takes about 32 bytes of stores per clock, so this is slow, but it sits in the slack
+            // before the next accumulator completes instead of in front of the operand loads.
+            const int chunk = lane & 7;
+#pragma unroll 1
+            for (int g = 0; g < Cfg::kGroups; ++g) {
+              const int col = n0 + g * 64 + chunk * 8;
+              if (n0 + g * 64 >= p.n) break;
+              const uint32_t buf = staging + g * kGroupBytes;
+              bf16* const out_base = reinterpret_cast<bf16*>(p.out) + (m0 + quarter * 32) * p.ldc + col;
 #pragma unroll
-              for (int g = 0; g < Cfg::kGroups; ++g) {
-                if (n0 + g * 64 < p.n) {
-                  ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
-                                    static_cast<int>(m0) + quarter * 32);
-                }
+              for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3);
+                uint4 raw;
+                ptx::ld_shared_v4(buf + r * kRowBytes + ((chunk ^ (r & 7)) << 4), raw);
+                if (col < p.n && m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(out_base + r * p.ldc) = raw;
               }
-              ptx::bulk_commit();
             }
+            __syncwarp();  // before the next tile's skip operand or results overwrite the buffers
           }
         }
       } else if constexpr (MODE != kRes) {
@@ -959,7 +913,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       prof_add(12, prof_ld);
       prof_add(13, prof_alu);
     }
-    if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
+    if (tma_path && !coalesced && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
   }
 
@@ -1008,6 +962,15 @@ bool pair_kernels_enabled() {
   return enabled;
 }
 
+// LC0B200_GEMM_TMA_STORE=1 in the environment keeps the TMA-store epilogue everywhere (measurement aid).
+bool tma_stores_forced() {
+  static const bool forced = []() {
+    const char* v = getenv("LC0B200_GEMM_TMA_STORE");
+    return v != nullptr && v[0] == '1';
+  }();
+  return forced;
+}
+
 // 2-D row-major tensor [rows, cols] with a row pitch, tiled into [box_rows, box_cols] boxes
 // whose inner extent is exactly 128 bytes (the swizzle span).
 bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows, long long cols,
@@ -1016,9 +979,9 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows
                            CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int BN, bool INT8, bool W_KN, int CTAS, int MODE, int SETS = 1>
+template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
 int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
-  using Cfg = TileCfg<BN, CTAS, MODE, SETS>;
+  using Cfg = TileCfg<BN, CTAS, MODE>;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;
   constexpr int kPanelN = INT8 ? 128 : 64;
   const int eb = INT8 ? 1 : 2;
@@ -1039,7 +1002,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
     if (!aligned16(g.res_skip_bf16) || (g.ld_skip % 8) != 0) return LC0B200_ERR_MISALIGNED;
     if (!make_map(&map_skip, g.res_skip_bf16, 2, g.m, g.n, g.ld_skip, 32, 64)) return LC0B200_ERR_CUDA;
   }
-  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE, SETS>;
+  auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -1065,6 +1028,8 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
              (g.ln_in_stats == nullptr || (aligned16(g.ln_in_c) && aligned16(g.ln_in_d))) &&
              (g.res_stats == nullptr || (aligned16(g.res_gamma_bf16) && aligned16(g.res_beta_bf16)));
   p.tma_store = tma_store ? 1 : 0;
+  // Short main loops are paced by the output itself: the asynchronous TMA store serves them better.
+  p.coalesced = (tma_store && (g.n % 8) == 0 && g.k > 512 && !tma_stores_forced()) ? 1 : 0;
   p.ln_in_stats = reinterpret_cast<const float2*>(g.ln_in_stats);
   p.ln_in_c = g.ln_in_c;
   p.ln_in_d = g.ln_in_d;
@@ -1116,12 +1081,6 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   int bn = 256;
   while (bn > kMinBn && (bn / 2 >= g.n || tiles(bn) < enough)) bn /= 2;
   if (bn == 256) {
-    if constexpr (MODE == kPlain && !INT8 && !W_KN) {
-      // Short K: the epilogue sets the pace; trade pipeline stages for a second set of staging buffers.
-      if (g.m >= kPairMinRows && g.k <= 512 && pair_kernels_enabled()) {
-        return launch<256, INT8, W_KN, 2, MODE, 2>(g, stream);
-      }
-    }
     if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
