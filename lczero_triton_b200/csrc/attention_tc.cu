@@ -128,13 +128,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      bool ok = true;
-      uint32_t i = 0;
-      for (long long pair = blockIdx.x; pair < p.pairs && ok; pair += gridDim.x, ++i) {
-        const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
-        ok = ptx::mbar_wait(bar_in_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x610u + s);
-        if (!ok) break;
+    // (The whole warp follows the loop and one elected lane issues: warp-uniform control flow lets
+    // the compiler keep addresses and descriptors in uniform registers.)
+    bool ok = true;
+    uint32_t i = 0;
+    for (long long pair = blockIdx.x; pair < p.pairs && ok; pair += gridDim.x, ++i) {
+      const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
+      ok = ptx::mbar_wait(bar_in_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x610u + s);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      if (ptx::elect_one()) {
         const uint32_t full = bar_in_full + 8 * s;
         ptx::mbar_expect_tx(full, 6 * kTileQ + (p.has_bias ? 2 * kTileBias : 0));
         const uint32_t st = stage_base + s * kStageBytes;
@@ -153,17 +156,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = ptx::instr_desc(1u, 1u, 0u, 128u, 128u);  // bf16 -> f32, A and B K-major
-      constexpr uint32_t idesc_o = ptx::instr_desc(1u, 1u, 1u, 128u, 32u);   // B (= V) MN-major
-      bool ok = true;
-      auto second_product = [&](uint32_t k) -> bool {
-        const uint32_t s = k % kStages, t = k & 1u;
-        if (!ptx::mbar_wait(bar_p_full + 8 * t, (k >> 1) & 1u, abort_flag, p.status, 0x640u + t)) return false;
-        if (!ptx::mbar_wait(bar_o_empty + 8 * t, ((k >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x650u + t)) return false;
-        ptx::tc_fence_after_sync();
-        const uint32_t v_addr = stage_base + s * kStageBytes + kOffV;
+    // ------------------------------------------------------------ MMA issuer (whole warp, one elected lane)
+    constexpr uint32_t idesc_s = ptx::instr_desc(1u, 1u, 0u, 128u, 128u);  // bf16 -> f32, A and B K-major
+    constexpr uint32_t idesc_o = ptx::instr_desc(1u, 1u, 1u, 128u, 32u);   // B (= V) MN-major
+    bool ok = true;
+    auto second_product = [&](uint32_t k) -> bool {
+      const uint32_t s = k % kStages, t = k & 1u;
+      bool good = ptx::mbar_wait(bar_p_full + 8 * t, (k >> 1) & 1u, abort_flag, p.status, 0x640u + t);
+      good = good && ptx::mbar_wait(bar_o_empty + 8 * t, ((k >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x650u + t);
+      if (!__all_sync(0xFFFFFFFFu, good)) return false;
+      ptx::tc_fence_after_sync();
+      const uint32_t v_addr = stage_base + s * kStageBytes + kOffV;
+      if (ptx::elect_one()) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {  // 16 keys per step; the two heads' keys are stacked
           const uint64_t da = ptx::smem_desc_sw128(p_base + t * kPOne + (j >> 2) * 16384 + (j & 3) * 32, 16, 1024);
@@ -173,17 +177,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ptx::tc_commit(bar_o_full + 8 * t);
         ptx::tc_commit(bar_in_empty + 8 * s);  // Q, K, V and the bias tiles of this stage are dead
         ptx::tc_commit(bar_p_empty + 8 * t);
-        return true;
-      };
-      uint32_t i = 0;
-      for (long long pair = blockIdx.x; pair < p.pairs && ok; pair += gridDim.x, ++i) {
-        const uint32_t s = i % kStages, t = i & 1u;
-        ok = ptx::mbar_wait(bar_in_full + 8 * s, (i / kStages) & 1u, abort_flag, p.status, 0x620u + s);
-        if (!ok) break;
-        ok = ptx::mbar_wait(bar_s_empty + 8 * t, ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x630u + t);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t st = stage_base + s * kStageBytes;
+      }
+      return true;
+    };
+    uint32_t i = 0;
+    for (long long pair = blockIdx.x; pair < p.pairs && ok; pair += gridDim.x, ++i) {
+      const uint32_t s = i % kStages, t = i & 1u;
+      ok = ptx::mbar_wait(bar_in_full + 8 * s, (i / kStages) & 1u, abort_flag, p.status, 0x620u + s);
+      ok = ok && ptx::mbar_wait(bar_s_empty + 8 * t, ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x630u + t);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t st = stage_base + s * kStageBytes;
+      if (ptx::elect_one()) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {  // depth 32 = two K steps of 16
           const uint64_t da = ptx::smem_desc_sw64(st + kOffQ + j * 32, 16, 512);
@@ -191,10 +197,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           ptx::mma_bf16(tmem_base + kColS + t * 128, da, db, idesc_s, j > 0 ? 1u : 0u);
         }
         ptx::tc_commit(bar_s_full + 8 * t);
-        if (i > 0) ok = second_product(i - 1);
       }
-      if (ok && i > 0) second_product(i - 1);
+      if (i > 0) ok = second_product(i - 1);
     }
+    if (ok && i > 0) second_product(i - 1);
     __syncwarp();
   } else {
     // ------------------------------------------------------------ softmax / epilogue: one score row per thread

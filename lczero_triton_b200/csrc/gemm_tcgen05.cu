@@ -785,14 +785,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                   pk[4 * c + 2], pk[4 * c + 3]);
               }
             }
-            if (!coalesced) {
-              ptx::fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                ptx::tma_store_2d(&map_out, buf, col0, static_cast<int>(m0) + quarter * 32);
-                ptx::bulk_commit();
-              }
-            }
             prof_alu += prof_now() - prof_g1;
             if (MODE == kRes) {
               // One partial per 64 output columns: part index col0 / 64, layout [part][row].
@@ -834,6 +826,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               }
             }
             __syncwarp();  // before the next tile's skip operand or results overwrite the buffers
+          } else if (n0 < p.n) {
+            // One proxy fence per tile and warp (by far the most expensive instruction here), then
+            // the stores of all groups; a group partly outside the matrix is clipped by the store.
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+              for (int g = 0; g < Cfg::kGroups; ++g) {
+                if (n0 + g * 64 < p.n) {
+                  ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
+                                    static_cast<int>(m0) + quarter * 32);
+                }
+              }
+              ptx::bulk_commit();
+            }
           }
         }
       } else if constexpr (MODE != kRes) {
@@ -1081,7 +1088,8 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   int bn = 256;
   while (bn > kMinBn && (bn / 2 >= g.n || tiles(bn) < enough)) bn /= 2;
   if (bn == 256) {
-    if (g.m >= kPairMinRows && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
+    // (Short main loops are paced by the output and measured faster on single CTAs.)
+    if (g.m >= kPairMinRows && g.k > 512 && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
   if constexpr (kMinBn <= 128) {
