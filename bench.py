@@ -207,7 +207,8 @@ def run(args) -> None:
     batch = args.batch
     peaks, peak_kind = _peaks()
     weights = random_weights(cfg, 0)
-    net = Bt4Net(weights, cfg, mode=args.mode)
+    deferred = None if args.deferred_ln < 0 else bool(args.deferred_ln)
+    net = Bt4Net(weights, cfg, mode=args.mode, deferred_layer_norm=deferred)
     masks_h, values_h = synthetic_planes(batch, seed=1000 + rank)
     masks_h, values_h = masks_h.pin_memory(), values_h.pin_memory()
     masks_d, values_d = masks_h.cuda(), values_h.cuda()
@@ -465,6 +466,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
     ap.add_argument("--graph", type=int, default=1, help="replay the forward from a CUDA graph in the timed loop")
+    ap.add_argument("--deferred-ln", type=int, default=-1,
+                    help="LayerNorm folded into the GEMM epilogues: 1 / 0, or -1 for the mode's default")
     ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm"],
                     help="measure one kernel instead of the whole forward pass")
     ap.add_argument("--m", type=int, default=262144)

@@ -227,51 +227,75 @@ __global__ void __launch_bounds__(kBlock) embed_concat_kernel(bf16* __restrict__
 }
 
 // Symmetric per-row int8 quantisation, one warp per row:
-// s = max|x| / 127 (1 when the row is all zero); q = clamp(rint(x / s), -127, 127).
+// s = max|x| / 127 (1 when the row is all zero); q = clamp(rint(x * (127 / max|x|)), -127, 127).
+// Rows up to 2048 wide stay in registers between the two passes.
+__device__ __forceinline__ uint2 quantize8(const uint4& raw, float inv) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    const int q0 = max(-127, min(127, __float2int_rn(f.x * inv)));
+    const int q1 = max(-127, min(127, __float2int_rn(f.y * inv)));
+    packed[j >> 1] |= (static_cast<uint32_t>(q0 & 0xFF) | (static_cast<uint32_t>(q1 & 0xFF) << 8)) << ((j & 1) * 16);
+  }
+  return make_uint2(packed[0], packed[1]);
+}
+
+__device__ __forceinline__ float amax8(const uint4& raw, float amax) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+  }
+  return amax;
+}
+
 __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
                                                                 const bf16* __restrict__ in, long long rows,
                                                                 int width, long long ld_in) {
+  constexpr int kHeld = 8;  // 16-byte groups a lane keeps in registers: 8 * 32 lanes * 8 values = 2048 columns
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kBlock / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const bf16* src = in + row * ld_in;
   int8_t* dst = out + row * width;
   const bool vec = ((width & 7) == 0) && ((ld_in & 7) == 0) && aligned16_dev(in) && aligned16_dev(out);
+  const int groups = width >> 3;
+  const bool held = vec && groups <= kHeld * 32;
+  uint4 keep[kHeld];
   float amax = 0.0f;
-  if (vec) {
-    for (int g = lane; g < (width >> 3); g += 32) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src) + g);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if (held) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w[j]);
-        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
+    for (int i = 0; i < kHeld; ++i) {
+      const int g = lane + 32 * i;
+      keep[i] = g < groups ? __ldg(reinterpret_cast<const uint4*>(src) + g) : make_uint4(0u, 0u, 0u, 0u);
+      amax = amax8(keep[i], amax);
     }
+  } else if (vec) {
+    for (int g = lane; g < groups; g += 32) amax = amax8(__ldg(reinterpret_cast<const uint4*>(src) + g), amax);
   } else {
     for (int c = lane; c < width; c += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[c])));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
   const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 1.0f;
   if (lane == 0) scale[row] = s;
-  if (vec) {
-    for (int g = lane; g < (width >> 3); g += 32) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src) + g);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-      uint32_t packed[2] = {0u, 0u};
+  if (held) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w[j]);
-        const int q0 = max(-127, min(127, __float2int_rn(__fdiv_rn(f.x, s))));
-        const int q1 = max(-127, min(127, __float2int_rn(__fdiv_rn(f.y, s))));
-        packed[j >> 1] |= (static_cast<uint32_t>(q0 & 0xFF) | (static_cast<uint32_t>(q1 & 0xFF) << 8)) << ((j & 1) * 16);
-      }
-      reinterpret_cast<uint2*>(dst)[g] = make_uint2(packed[0], packed[1]);
+    for (int i = 0; i < kHeld; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups) reinterpret_cast<uint2*>(dst)[g] = quantize8(keep[i], inv);
+    }
+  } else if (vec) {
+    for (int g = lane; g < groups; g += 32) {
+      reinterpret_cast<uint2*>(dst)[g] = quantize8(__ldg(reinterpret_cast<const uint4*>(src) + g), inv);
     }
   } else {
     for (int c = lane; c < width; c += 32) {
-      const int q = max(-127, min(127, __float2int_rn(__fdiv_rn(__bfloat162float(src[c]), s))));
+      const int q = max(-127, min(127, __float2int_rn(__bfloat162float(src[c]) * inv)));
       dst[c] = static_cast<int8_t>(q);
     }
   }

@@ -47,6 +47,16 @@ constexpr int kGroupBytes = 32 * kRowBytes;  // staging for 32 rows x 64 bf16 co
 //   kRes  : y = alpha * (dequant(acc) + bias) + skip, skip plain or a deferred LayerNorm; row sums out
 enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 
+// How the grouped epilogue (bf16 results, 64-column groups) gets a tile to global memory:
+//   kStoreTma   : staged in shared memory, TMA store (any row length a tensor map takes; asynchronous,
+//                 but its shared-memory reads compete with the tensor core's operand reads: about
+//                 1100 clocks per 128 x 256 tile)
+//   kStoreDirect: straight from registers, 32 bytes (one sector) per lane and store; touches no shared
+//                 memory, but the epilogue warps wait on the store path (a row per lane drains slowly)
+// Measured per shape (a third way, warps copying the staged tile out in 128-byte lines, never won):
+// TMA wins except where the main loop is long enough to hide the slower stores.
+enum : int { kStoreTma = 0, kStoreDirect = 2 };
+
 template <int BN, int CTAS, int MODE>
 struct TileCfg {
   static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
@@ -93,7 +103,7 @@ struct KernelParams {
   int activation;
   int vec_ok;     // out / bias / scales / fold vectors are 16-byte aligned and ldc keeps rows aligned
   int tma_store;  // bf16 output that a tensor map can address (map_out is valid)
-  int coalesced;  // ... whose rows also split into whole 16-byte pieces: the warps copy the staging buffers out
+  int store_mode;  // how the grouped epilogue writes its results: kStoreTma or kStoreDirect
   unsigned int* status;
   // Deferred LayerNorm (see lc0b200_gemm_args).
   const float2* ln_in_stats;
@@ -641,7 +651,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t staging_warp = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
     const uint32_t skip_bar = bar_skip + 8 * ew;
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;  // grouped epilogue
-    const bool coalesced = p.coalesced != 0;  // ... copied out by the warp itself (else by TMA store)
+    const int store_mode = p.store_mode;
+    const bool direct = store_mode == kStoreDirect;
+    const bool staged = !direct;  // results pass through the staging buffers
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
@@ -693,7 +705,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       rc.nmean = (MODE == kRes) ? -rc.mean * rc.rstd : -rc.mean;
-      if (tma_path && !coalesced) {
+      if (tma_path && store_mode == kStoreTma) {
         // TMA-store flavour: the staging buffers are free once the previous tile's stores have
         // finished reading them.
         if (lane == 0) ptx::bulk_wait_read<0>();
@@ -702,7 +714,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if constexpr (MODE == kRes) {
         // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
         // buffers, one 32 x 64 box per group.
-        if (coalesced) {
+        if (store_mode != kStoreTma) {
           // The buffers were last written and read by ordinary shared-memory accesses of this warp.
           ptx::fence_proxy_async_smem();
           __syncwarp();
@@ -747,17 +759,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool released = false;  // accumulator already handed back to the MMA issuer
       if (tma_path) {
         if constexpr (Cfg::kTmaStore) {
+          int groups_here = (p.n - n0 + 63) >> 6;  // groups of this warp that reach into the matrix
+          groups_here = groups_here < 0 ? 0 : (groups_here > Cfg::kGroups ? Cfg::kGroups : groups_here);
+          if (groups_here == 0) {  // nothing to read: hand the accumulator straight back
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if (CTAS == 2) ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_acc_empty + 8 * acc, 0u));
+              else ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+            }
+          }
 #pragma unroll 1
-          for (int g = 0; g < Cfg::kGroups; ++g) {
-            const int col0 = n0 + g * 64;
-            if (col0 >= p.n) break;  // warp-uniform; a partly outside group is clipped by the store
+          for (int g = 0; g < groups_here; ++g) {
+            const int col0 = n0 + g * 64;  // a partly outside group is clipped by the store
             uint32_t v[64];
             const long long prof_g0 = prof_now();
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             ptx::tc_wait_ld();
+            if (g == groups_here - 1) {
+              // The last of this warp's accumulator columns are in registers: hand the accumulator
+              // back to the MMA issuer before the arithmetic and the stores of this group.
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) {
+                if (CTAS == 2) {
+                  ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_acc_empty + 8 * acc, 0u));  // the leader's barrier
+                } else {
+                  ptx::mbar_arrive(bar_acc_empty + 8 * acc);
+                }
+              }
+            }
             const long long prof_g1 = prof_now();
             prof_ld += prof_g1 - prof_g0;
+            bf16* const out_row = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;  // direct stores
             float sum = 0.0f, sumsq = 0.0f;
             // Row `lane` of this group's 32 x 128-byte staging buffer (skip operand in, results out)
             // in the 128-byte swizzle the tensor maps use: 16-byte chunk c of row r lives at
@@ -779,10 +814,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               uint32_t pk[16];
               finish32_sv<MODE, INT8, BN>(&v[h * 32], pk, skip_raw, rc, p, sum, sumsq, vec_base,
                                           half * kColsPerWarp + g * 64 + h * 32);
+              if (staged) {
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
-                                  pk[4 * c + 2], pk[4 * c + 3]);
+                for (int c = 0; c < 4; ++c) {
+                  ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
+                                    pk[4 * c + 2], pk[4 * c + 3]);
+                }
+              } else if (row_ok) {
+                // n is a multiple of 16 here: each 16-column piece is wholly inside or outside.
+                if (col0 + h * 32 < p.n) ptx::st_global_v8(out_row + h * 32, &pk[0]);
+                if (col0 + h * 32 + 16 < p.n) ptx::st_global_v8(out_row + h * 32 + 16, &pk[8]);
               }
             }
             prof_alu += prof_now() - prof_g1;
@@ -791,42 +832,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
             }
           }
-          // TMEM has been read out: hand the accumulator back.
-          ptx::tc_fence_before_sync();
+          // The column vectors have been read for the last time.
           __syncwarp();
-          if (lane == 0) {
-            if (CTAS == 2) {
-              ptx::mbar_arrive_cluster(ptx::map_to_cta(bar_acc_empty + 8 * acc, 0u));  // the leader's barrier
-            } else {
-              ptx::mbar_arrive(bar_acc_empty + 8 * acc);
-            }
-            ptx::mbar_arrive(bar_vec_free);
-          }
+          if (lane == 0) ptx::mbar_arrive(bar_vec_free);
           released = true;
           prof_math += prof_now() - prof_t1;
-          if (coalesced) {
-            // Copy the tile out of the staging buffers, now that the accumulator is back with the MMA
-            // issuer: 8 lanes per row (eight 16-byte chunks = one 128-byte line), 4 rows per
-            // instruction.  n is a multiple of 8 here, so a chunk is wholly inside or outside.  The
-            // SM takes about 32 bytes of stores per clock, so this is slow, but it sits in the slack
-            // before the next accumulator completes instead of in front of the operand loads.
-            const int chunk = lane & 7;
-#pragma unroll 1
-            for (int g = 0; g < Cfg::kGroups; ++g) {
-              const int col = n0 + g * 64 + chunk * 8;
-              if (n0 + g * 64 >= p.n) break;
-              const uint32_t buf = staging + g * kGroupBytes;
-              bf16* const out_base = reinterpret_cast<bf16*>(p.out) + (m0 + quarter * 32) * p.ldc + col;
-#pragma unroll
-              for (int it = 0; it < 8; ++it) {
-                const int r = it * 4 + (lane >> 3);
-                uint4 raw;
-                ptx::ld_shared_v4(buf + r * kRowBytes + ((chunk ^ (r & 7)) << 4), raw);
-                if (col < p.n && m0 + quarter * 32 + r < p.m) *reinterpret_cast<uint4*>(out_base + r * p.ldc) = raw;
-              }
-            }
-            __syncwarp();  // before the next tile's skip operand or results overwrite the buffers
-          } else if (n0 < p.n) {
+          if (store_mode == kStoreTma && n0 < p.n) {
             // One proxy fence per tile and warp (by far the most expensive instruction here), then
             // the stores of all groups; a group partly outside the matrix is clipped by the store.
             ptx::fence_proxy_async_smem();
@@ -920,7 +931,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       prof_add(12, prof_ld);
       prof_add(13, prof_alu);
     }
-    if (tma_path && !coalesced && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
+    if (tma_path && store_mode == kStoreTma && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
   }
 
@@ -969,13 +980,17 @@ bool pair_kernels_enabled() {
   return enabled;
 }
 
-// LC0B200_GEMM_TMA_STORE=1 in the environment keeps the TMA-store epilogue everywhere (measurement aid).
-bool tma_stores_forced() {
-  static const bool forced = []() {
-    const char* v = getenv("LC0B200_GEMM_TMA_STORE");
-    return v != nullptr && v[0] == '1';
+// LC0B200_GEMM_STORE=tma|direct in the environment forces one store mode wherever the output
+// allows it (measurement aid); unset, the mode follows the shape.
+int forced_store_mode() {
+  static const int mode = []() {
+    const char* v = getenv("LC0B200_GEMM_STORE");
+    if (v == nullptr) return -1;
+    if (v[0] == 't') return static_cast<int>(kStoreTma);
+    if (v[0] == 'd') return static_cast<int>(kStoreDirect);
+    return -1;
   }();
-  return forced;
+  return mode;
 }
 
 // 2-D row-major tensor [rows, cols] with a row pitch, tiled into [box_rows, box_cols] boxes
@@ -1035,8 +1050,12 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
              (g.ln_in_stats == nullptr || (aligned16(g.ln_in_c) && aligned16(g.ln_in_d))) &&
              (g.res_stats == nullptr || (aligned16(g.res_gamma_bf16) && aligned16(g.res_beta_bf16)));
   p.tma_store = tma_store ? 1 : 0;
-  // Short main loops are paced by the output itself: the asynchronous TMA store serves them better.
-  p.coalesced = (tma_store && (g.n % 8) == 0 && g.k > 512 && !tma_stores_forced()) ? 1 : 0;
+  // Store mode of the grouped epilogue: see kStoreTma / kStoreDirect.
+  const bool direct_ok = tma_store && (reinterpret_cast<uintptr_t>(g.out) & 31u) == 0 && (g.ldc % 16) == 0 && (g.n % 16) == 0;
+  int mode = (g.k >= 1536 && direct_ok) ? kStoreDirect : kStoreTma;
+  const int forced = forced_store_mode();
+  if (forced == kStoreTma || (forced == kStoreDirect && direct_ok)) mode = forced;
+  p.store_mode = mode;
   p.ln_in_stats = reinterpret_cast<const float2*>(g.ln_in_stats);
   p.ln_in_c = g.ln_in_c;
   p.ln_in_d = g.ln_in_d;

@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(co
   if (p.q_out != nullptr) {
     amax = warp_max(amax);
     const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 1.0f;
     if (lane == 0) p.q_scale[row] = s;
     uint2* qdst = reinterpret_cast<uint2*>(p.q_out + row * p.width);
 #pragma unroll
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(co
         uint32_t packed[2] = {0u, 0u};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int q = max(-127, min(127, __float2int_rn(__fdiv_rn(v[g][j], s))));
+          const int q = max(-127, min(127, __float2int_rn(v[g][j] * inv)));
           packed[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << ((j & 3) * 8);
         }
         qdst[idx] = make_uint2(packed[0], packed[1]);

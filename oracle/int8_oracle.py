@@ -8,7 +8,8 @@ project's own specification:
   column is all zero), ``Wq[k,n] = clamp(rint(W[k,n] / s_w[n]), -127, 127)``;
 * activations, symmetric per token row, from the bf16 values the GPU stores:
   ``s_a[m] = max_k |A[m,k]| / 127`` (1 if the row is all zero),
-  ``Aq[m,k] = clamp(rint(A[m,k] / s_a[m]), -127, 127)``;
+  ``Aq[m,k] = clamp(rint(A[m,k] * (127 / max_k |A[m,k]|)), -127, 127)`` (one division per row; the
+  factor is 1 for an all-zero row);
 * ``rint`` is round-half-to-even, all arithmetic in IEEE fp32;
 * ``acc[m,n] = sum_k int32(Aq[m,k]) * int32(Wq[k,n])`` exactly;
 * ``y[m,n] = act((float(acc[m,n]) * s_a[m]) * s_w[n] + bias[n])``.
@@ -35,7 +36,9 @@ def quantize_rows(a: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     x = a.float()
     amax = x.abs().amax(dim=1)
     scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
-    return torch.clamp(torch.round(x / scale[:, None]), -127, 127).to(torch.int8), scale
+    # (torch evaluates ``127.0 / t`` as ``t.reciprocal() * 127.0``: divide two tensors for one rounding.)
+    inv = torch.where(amax > 0, torch.full_like(amax, 127.0) / amax, torch.ones_like(amax))
+    return torch.clamp(torch.round(x * inv[:, None]), -127, 127).to(torch.int8), scale
 
 
 def int_matmul(aq: torch.Tensor, wq_kn: torch.Tensor) -> torch.Tensor:
