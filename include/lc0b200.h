@@ -57,9 +57,10 @@ enum { LC0B200_W_KN = 0, LC0B200_W_NK = 1 };
 
 LC0B200_API const char* lc0b200_version(void);
 LC0B200_API const char* lc0b200_status_string(int status);
-/* Synchronises the current device and returns LC0B200_ERR_DEVICE_TIMEOUT if any kernel's
- * bounded wait ran out since the last call (detail_host[0..3] receives the flag words,
- * may be NULL); clears the flag. */
+/* Synchronises the current device and returns LC0B200_ERR_DEVICE_TIMEOUT if any kernel gave up
+ * since the last call (detail_host[0..3] receives the flag words, may be NULL); clears the flag.
+ * Word 0 says why: 1 = a bounded wait ran out (word 1 = which wait, word 2 = CTA), 2 = a kernel
+ * found its shared-memory window not 1024-byte aligned and did nothing (word 1 = the address). */
 LC0B200_API int lc0b200_device_status(unsigned int* detail_host);
 
 /* ---- layout and element-wise ops ------------------------------------------------------ */

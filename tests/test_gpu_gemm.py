@@ -90,6 +90,25 @@ def test_bf16_gemm_bias_activation_epilogue(ops, activation) -> None:
     torch.testing.assert_close(out.float().cpu(), want, rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize(("m", "n", "k"), [(300, 400, 1600), (300, 408, 1600), (8300, 1040, 1536), (257, 272, 2048),
+                                            (8300, 1040, 1024)])
+def test_bf16_gemm_store_paths_at_matrix_edges(ops, m, n, k) -> None:
+    """Long K takes the stores straight from registers (rows in whole 32-byte pieces), everything else
+    the staged TMA store; both must respect a row pitch, ragged last tiles and leave neighbours alone."""
+    from lczero_triton_b200 import _lib
+
+    a, w = _operands(m, n, k, 125)
+    a, w = (a.float() * 0.2).to(BF16), (w.float() * 0.2).to(BF16)
+    bias = (torch.randn(n, generator=_gen(126)) * 0.5).to(BF16)
+    want = O.activate(O.matmul(a, w) + bias.float(), "mish")
+    pitch = n + 48
+    wide = torch.full((m + 3, pitch), 7.0, dtype=BF16, device="cuda")
+    ops.gemm(wide[:m, 16:16 + n], a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, bias=bias.cuda(), activation="mish",
+             ldc=pitch, w_layout=_lib.W_NK)
+    torch.testing.assert_close(wide[:m, 16:16 + n].float().cpu(), want, rtol=1e-2, atol=1e-2)
+    assert (wide[:m, :16] == 7.0).all() and (wide[:m, 16 + n:] == 7.0).all() and (wide[m:] == 7.0).all()
+
+
 def test_bf16_gemm_strided_output_and_f32_output(ops) -> None:
     from lczero_triton_b200 import _lib
 
