@@ -55,7 +55,8 @@ enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 //                 memory, but the epilogue warps wait on the store path (a row per lane drains slowly)
 // Measured per shape (a third way, warps copying the staged tile out in 128-byte lines, never won):
 // TMA wins except where the main loop is long enough to hide the slower stores.
-enum : int { kStoreTma = 0, kStoreDirect = 2 };
+//   kStoreMixed : even groups staged and stored by TMA, odd groups straight from registers: half of each cost
+enum : int { kStoreTma = 0, kStoreMixed = 1, kStoreDirect = 2 };
 
 template <int BN, int CTAS, int MODE>
 struct TileCfg {
@@ -652,8 +653,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t skip_bar = bar_skip + 8 * ew;
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;  // grouped epilogue
     const int store_mode = p.store_mode;
-    const bool direct = store_mode == kStoreDirect;
-    const bool staged = !direct;  // results pass through the staging buffers
+    const bool any_staged = store_mode != kStoreDirect;  // some results pass through the staging buffers
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
@@ -705,8 +705,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       rc.nmean = (MODE == kRes) ? -rc.mean * rc.rstd : -rc.mean;
-      if (tma_path && store_mode == kStoreTma) {
-        // TMA-store flavour: the staging buffers are free once the previous tile's stores have
+      if (tma_path && any_staged) {
+        // TMA-store flavours: the staging buffers are free once the previous tile's stores have
         // finished reading them.
         if (lane == 0) ptx::bulk_wait_read<0>();
         __syncwarp();
@@ -715,7 +715,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
         // buffers, one 32 x 64 box per group.
         if (store_mode != kStoreTma) {
-          // The buffers were last written and read by ordinary shared-memory accesses of this warp.
+          // Some buffers were last read by ordinary shared-memory loads of this warp only.
           ptx::fence_proxy_async_smem();
           __syncwarp();
         }
@@ -793,6 +793,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const long long prof_g1 = prof_now();
             prof_ld += prof_g1 - prof_g0;
             bf16* const out_row = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;  // direct stores
+            const bool staged = store_mode == kStoreTma || (store_mode == kStoreMixed && (g & 1) == 0);
             float sum = 0.0f, sumsq = 0.0f;
             // Row `lane` of this group's 32 x 128-byte staging buffer (skip operand in, results out)
             // in the 128-byte swizzle the tensor maps use: 16-byte chunk c of row r lives at
@@ -837,7 +838,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (lane == 0) ptx::mbar_arrive(bar_vec_free);
           released = true;
           prof_math += prof_now() - prof_t1;
-          if (store_mode == kStoreTma && n0 < p.n) {
+          if (any_staged && n0 < p.n) {
             // One proxy fence per tile and warp (by far the most expensive instruction here), then
             // the stores of all groups; a group partly outside the matrix is clipped by the store.
             ptx::fence_proxy_async_smem();
@@ -845,7 +846,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) {
 #pragma unroll
               for (int g = 0; g < Cfg::kGroups; ++g) {
-                if (n0 + g * 64 < p.n) {
+                if (n0 + g * 64 < p.n && (store_mode == kStoreTma || (g & 1) == 0)) {
                   ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
                                     static_cast<int>(m0) + quarter * 32);
                 }
@@ -931,7 +932,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       prof_add(12, prof_ld);
       prof_add(13, prof_alu);
     }
-    if (tma_path && store_mode == kStoreTma && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
+    if (tma_path && any_staged && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
   }
 
@@ -980,13 +981,14 @@ bool pair_kernels_enabled() {
   return enabled;
 }
 
-// LC0B200_GEMM_STORE=tma|direct in the environment forces one store mode wherever the output
+// LC0B200_GEMM_STORE=tma|mixed|direct in the environment forces one store mode wherever the output
 // allows it (measurement aid); unset, the mode follows the shape.
 int forced_store_mode() {
   static const int mode = []() {
     const char* v = getenv("LC0B200_GEMM_STORE");
     if (v == nullptr) return -1;
     if (v[0] == 't') return static_cast<int>(kStoreTma);
+    if (v[0] == 'm') return static_cast<int>(kStoreMixed);
     if (v[0] == 'd') return static_cast<int>(kStoreDirect);
     return -1;
   }();
@@ -1054,7 +1056,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   const bool direct_ok = tma_store && (reinterpret_cast<uintptr_t>(g.out) & 31u) == 0 && (g.ldc % 16) == 0 && (g.n % 16) == 0;
   int mode = (g.k >= 1536 && direct_ok) ? kStoreDirect : kStoreTma;
   const int forced = forced_store_mode();
-  if (forced == kStoreTma || (forced == kStoreDirect && direct_ok)) mode = forced;
+  if (forced == kStoreTma || ((forced == kStoreDirect || forced == kStoreMixed) && direct_ok)) mode = forced;
   p.store_mode = mode;
   p.ln_in_stats = reinterpret_cast<const float2*>(g.ln_in_stats);
   p.ln_in_c = g.ln_in_c;
