@@ -18,6 +18,7 @@
 #ifndef LC0B200_H_
 #define LC0B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__GNUC__)
@@ -253,6 +254,48 @@ LC0B200_API int lc0b200_policy_tail(float* out_f32, const void* records_bf16, co
 LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits,
                                  const float* wdl_logits, const uint8_t* legal_mask, int batch_size,
                                  int policy_size, void* stream);
+
+/* ---- the whole forward pass as one object -------------------------------------------------
+ *
+ * What an engine written in C or C++ binds instead of the per-operator entry points: the role of the
+ * reference's runtime (LC0EX_BACKEND_BENCHMARK.md:125-139: persistent buffers kept by name, one kernel
+ * launch per graph node) for the graph of N:343-1550.  Shapes are the reference's layer sizes; weights
+ * go in under the reference's canonical buffer names (every `name=` of N:343-1466, e.g.
+ * "/encoder0/mha/Q/w/w") as bf16 in its input-major [K,N] layout, one-element constants
+ * ("/encoder0/alpha*input/w", "/policy/scale/w", ...) included.  bf16 arithmetic, encoder LayerNorms
+ * folded into the GEMM epilogues.  head depth (embedding / heads) must be 32.
+ *
+ * All device memory is ONE caller-provided arena of lc0b200_net_arena_bytes() bytes (256-byte aligned):
+ * weights as uploaded, the operands derived from them and the workspace for max_batch positions.
+ * create / destroy allocate and free only a small host structure.  set_weight copies host memory to the
+ * arena on `stream`; finalize derives the GEMM operands (transposes, LayerNorm folding) and synchronises
+ * `stream` once; forward only launches (about 185 kernels at 15 layers) and neither allocates nor
+ * synchronises, so it can be captured into a CUDA graph.  One forward at a time per network object. */
+typedef struct lc0b200_net lc0b200_net;
+typedef struct lc0b200_net_config {
+  int embedding, layers, heads, ffn;
+  int pos_enc;                                        /* positional-encoding channels per square */
+  int smolgen_compress, smolgen_hidden, smolgen_gen;  /* channels per token, dense1 width, per-head width */
+  int policy, policy_model;                           /* policy embedding and query/key widths */
+  int value_embed, value_hidden, mlh_embed, mlh_hidden;
+  float ln_eps;
+} lc0b200_net_config;
+LC0B200_API size_t lc0b200_net_arena_bytes(const lc0b200_net_config* config, int max_batch); /* 0 = bad config */
+LC0B200_API int lc0b200_net_create(lc0b200_net** out, const lc0b200_net_config* config, int max_batch,
+                                   void* device_arena, size_t arena_bytes);
+LC0B200_API void lc0b200_net_destroy(lc0b200_net* net);
+/* The buffers the network expects: index < lc0b200_net_weight_count(); *name stays valid while net lives. */
+LC0B200_API int lc0b200_net_weight_count(const lc0b200_net* net);
+LC0B200_API int lc0b200_net_weight_info(const lc0b200_net* net, int index, const char** name, long long* elements);
+/* LC0B200_ERR_UNSUPPORTED: no such buffer; LC0B200_ERR_BAD_SHAPE: wrong element count. */
+LC0B200_API int lc0b200_net_set_weight(lc0b200_net* net, const char* name, const void* host_bf16, long long elements,
+                                       void* stream);
+/* LC0B200_ERR_NULL_POINTER while any buffer is still missing. */
+LC0B200_API int lc0b200_net_finalize(lc0b200_net* net, void* stream);
+/* masks u64[batch,112], values f32[batch,112] (N:328-340) -> policy f32[batch,1858], raw WDL logits
+ * f32[batch,3], moves left f32[batch,1]; all device pointers; batch <= max_batch. */
+LC0B200_API int lc0b200_net_forward(lc0b200_net* net, const uint64_t* masks, const float* values, int batch,
+                                    float* policy_f32, float* wdl_f32, float* mlh_f32, void* stream);
 
 #ifdef __cplusplus
 }

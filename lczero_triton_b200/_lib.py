@@ -70,7 +70,17 @@ SIGNATURES: dict[str, tuple] = {
     "lc0b200_embed_concat": (_P, _P, _P, _P, _I, _I, _P),
     "lc0b200_policy_tail": (_P, _P, _P, _P, _P, _I, _I, _P),
     "lc0b200_output_probabilities": (_P, _P, _P, _P, _P, _I, _I, _P),
+    "lc0b200_net_arena_bytes": (_P, _I),
+    "lc0b200_net_create": (POINTER(c_void_p), _P, _I, _P, ctypes.c_size_t),
+    "lc0b200_net_destroy": (_P,),
+    "lc0b200_net_weight_count": (_P,),
+    "lc0b200_net_weight_info": (_P, _I, POINTER(c_char_p), POINTER(c_longlong)),
+    "lc0b200_net_set_weight": (_P, c_char_p, _P, _L, _P),
+    "lc0b200_net_finalize": (_P, _P),
+    "lc0b200_net_forward": (_P, _P, _P, _I, _P, _P, _P, _P),
 }
+# Return types other than the int status.
+RESTYPES = {"lc0b200_net_arena_bytes": ctypes.c_size_t, "lc0b200_net_destroy": None}
 STRING_GETTERS = ("lc0b200_version", "lc0b200_status_string")
 
 _lib: ctypes.CDLL | None = None
@@ -89,7 +99,7 @@ def load() -> ctypes.CDLL:
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = list(argtypes)
-        fn.restype = c_int
+        fn.restype = RESTYPES.get(name, c_int)
     lib.lc0b200_version.argtypes = []
     lib.lc0b200_version.restype = c_char_p
     lib.lc0b200_status_string.argtypes = [c_int]

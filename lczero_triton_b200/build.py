@@ -15,7 +15,7 @@ PACKAGE_DIR = pathlib.Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "liblc0b200.so"
 SOURCES = ("api.cu", "gemm_tcgen05.cu", "gemm_simt.cu", "elementwise.cu", "layernorm.cu", "attention.cu", "attention_tc.cu", "policy.cu",
-           "no_alloc.cu")
+           "no_alloc.cu", "net_runtime.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--threads", "0",

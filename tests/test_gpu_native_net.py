@@ -1,0 +1,108 @@
+"""The network object of the C ABI (``lc0b200_net_*``): the whole forward pass driven from C.
+
+It must give what ``net.Bt4Net`` gives (the same kernels in the same order; only the upload-time
+LayerNorm folding is summed in another order) and meet the fp32 oracle's tolerance on its own.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+from oracle import bt4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    from lczero_triton_b200 import build
+
+    build.build()
+    from lczero_triton_b200 import _lib, config, mapping_table, native, net, synthetic, weights
+
+    return {"config": config, "net": net, "native": native, "synthetic": synthetic, "weights": weights, "lib": _lib,
+            "table": torch.tensor(mapping_table.values(), dtype=torch.int32)}
+
+
+def _within_tolerance(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
+    err = (got - want).abs()
+    return (err <= 1e-2) | (err <= 1e-2 * want.abs())
+
+
+def _no_timeouts(pkg) -> None:
+    status, detail = pkg["lib"].device_status()
+    assert status == 0, f"a kernel gave up: {detail}"
+
+
+@pytest.mark.parametrize("batch", [1, 5, 32])
+def test_tiny_network_through_the_c_object(pkg, batch) -> None:
+    cfg = pkg["config"].TINY
+    weights = pkg["weights"].random_weights(cfg, 3)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, 3)
+    native = pkg["native"].NativeNet(weights, cfg, max_batch=32)
+    policy, wdl, mlh = (x.cpu() for x in native.forward(masks.cuda(), values.cuda()))
+    _no_timeouts(pkg)
+    want_policy, want_wdl, want_mlh = O.forward(weights, cfg, masks, values, table=pkg["table"])
+    assert _within_tolerance(policy, want_policy).all()
+    assert _within_tolerance(wdl, want_wdl).all()
+    assert _within_tolerance(mlh, want_mlh).all()
+    # against the Python-driven network: same kernels, same order
+    ref = pkg["net"].Bt4Net(weights, cfg)
+    ref_policy, ref_wdl, ref_mlh = (x.cpu() for x in ref.forward(masks.cuda(), values.cuda()))
+    torch.testing.assert_close(policy, ref_policy, rtol=2e-2, atol=2e-3)
+    torch.testing.assert_close(wdl, ref_wdl, rtol=2e-2, atol=2e-3)
+    torch.testing.assert_close(mlh, ref_mlh, rtol=2e-2, atol=2e-3)
+    native.close()
+
+
+def test_bt4_shape_through_the_c_object_matches_the_python_network(pkg) -> None:
+    cfg = pkg["config"].BT4
+    batch = 8
+    weights = pkg["weights"].random_weights(cfg, 1)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, 1)
+    native = pkg["native"].NativeNet(weights, cfg, max_batch=16)
+    got = [x.cpu() for x in native.forward(masks.cuda(), values.cuda())]
+    # a second call reuses the workspace and must reproduce the first bit for bit
+    again = [x.cpu() for x in native.forward(masks.cuda(), values.cuda())]
+    _no_timeouts(pkg)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b)
+    # Two bf16 evaluations of fifteen layers differ by rounding flips that the layers amplify (the folded
+    # LayerNorm vectors are summed in another order): hold both to the oracle's bound, and each other to
+    # half of it.
+    ref = pkg["net"].Bt4Net(weights, cfg)
+    python_net = [x.cpu() for x in ref.forward(masks.cuda(), values.cuda())]
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"])
+    for a, b, w in zip(got, python_net, want):
+        spread = float(w.std().clamp_min(1e-6))
+        assert _within_tolerance(a, w).all()
+        assert float((a - w).abs().max()) < 0.3 * spread
+        assert float((a - b).abs().max()) < 0.15 * spread + 2e-3
+    native.close()
+
+
+def test_object_rejects_misuse(pkg) -> None:
+    lib = pkg["lib"].load()
+    cfg = pkg["config"].TINY
+    cfg_c = pkg["native"].NetConfigC.from_config(cfg)
+    nbytes = lib.lc0b200_net_arena_bytes(ctypes.byref(cfg_c), 4)
+    assert nbytes > 0
+    arena = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    handle = ctypes.c_void_p()
+    assert lib.lc0b200_net_create(ctypes.byref(handle), ctypes.byref(cfg_c), 4, arena.data_ptr(), nbytes - 4096) == 7
+    assert lib.lc0b200_net_create(ctypes.byref(handle), ctypes.byref(cfg_c), 4, arena.data_ptr(), nbytes) == 0
+    host = torch.zeros(16, dtype=torch.bfloat16)
+    assert lib.lc0b200_net_set_weight(handle, b"/no/such/buffer", host.data_ptr(), 16, None) == 3
+    assert lib.lc0b200_net_set_weight(handle, b"/attn_body/add/w", host.data_ptr(), 16, None) == 2
+    assert lib.lc0b200_net_finalize(handle, None) == 1          # weights missing
+    out = torch.empty(4 * 1858, dtype=torch.float32, device="cuda")
+    planes = torch.zeros((4, 112), dtype=torch.int64, device="cuda")
+    assert lib.lc0b200_net_forward(handle, planes.data_ptr(), planes.data_ptr(), 4, out.data_ptr(), out.data_ptr(),
+                                   out.data_ptr(), None) == 3  # not finalised
+    lib.lc0b200_net_destroy(handle)
+    bad = pkg["native"].NetConfigC.from_config(cfg)
+    bad.heads = 3
+    assert lib.lc0b200_net_arena_bytes(ctypes.byref(bad), 4) == 0
