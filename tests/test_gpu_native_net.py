@@ -61,8 +61,8 @@ def test_tiny_network_through_the_c_object(pkg, batch) -> None:
 def test_bt4_shape_through_the_c_object_matches_the_python_network(pkg) -> None:
     cfg = pkg["config"].BT4
     batch = 8
-    weights = pkg["weights"].random_weights(cfg, 1)
-    masks, values = pkg["synthetic"].synthetic_planes(batch, 1)
+    weights = pkg["weights"].random_weights(cfg, 0)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, 0)
     native = pkg["native"].NativeNet(weights, cfg, max_batch=16)
     got = [x.cpu() for x in native.forward(masks.cuda(), values.cuda())]
     # a second call reuses the workspace and must reproduce the first bit for bit
