@@ -77,3 +77,38 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path) -> None:
     monkeypatch.setattr(_lib, "LIBRARY_PATH", tmp_path / "absent.so")
     with pytest.raises(_lib.Lc0B200Error, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+C_CALLER = r"""
+#include <stdio.h>
+#include "lc0b200.h"
+int main(void) {
+  lc0b200_net_config cfg = {128, 4, 4, 256, 64, 16, 64, 64, 128, 128, 128, 128, 32, 128, 1e-3f};
+  size_t bytes = lc0b200_net_arena_bytes(&cfg, 32);
+  lc0b200_gemm_args args = {0};
+  printf("%zu %d %d %s\n", bytes, lc0b200_gemm(&args, NULL),
+         lc0b200_net_forward(NULL, NULL, NULL, 1, NULL, NULL, NULL, NULL), lc0b200_version());
+  return bytes > 0 ? 0 : 1;
+}
+"""
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(lib, tmp_path) -> None:
+    """The boundary is a C ABI: a C11 translation unit includes the header, links against the
+    library and calls it (no device needed for what it calls)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    source = tmp_path / "caller.c"
+    source.write_text(C_CALLER)
+    exe = tmp_path / "caller"
+    libdir = _lib.LIBRARY_PATH.parent
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(source), "-o", str(exe),
+                    "-L", str(libdir), "-l:liblc0b200.so", f"-Wl,-rpath,{libdir}"], check=True)
+    done = subprocess.run([str(exe)], check=True, capture_output=True, text=True)
+    fields = done.stdout.split()
+    assert int(fields[0]) > 1_000_000 and fields[3].startswith("lc0b200")
+    assert fields[1] == "1" and fields[2] == "1"  # null pointers are refused with a status, not a crash
