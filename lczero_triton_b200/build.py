@@ -6,6 +6,8 @@
 
 from __future__ import annotations
 
+import fcntl
+import os
 import pathlib
 import shutil
 import subprocess
@@ -42,15 +44,27 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     """Compile the library if any source is newer than it; return its path."""
     if not force and not needs_build():
         return LIBRARY
-    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", str(LIBRARY), *[str(CSRC / s) for s in SOURCES]]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    result = subprocess.run(cmd, capture_output=True, text=True, check=False)
-    if result.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{result.stdout}\n{result.stderr}")
-    if verbose:
-        print(result.stderr)
+    # Several ranks of one job may get here together: one builds (into a temporary file that is
+    # renamed into place), the others wait on the lock and then find the library up to date.
+    with open(PACKAGE_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():
+                return LIBRARY
+            scratch = LIBRARY.with_suffix(f".so.tmp{os.getpid()}")
+            cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", str(scratch), *[str(CSRC / s) for s in SOURCES]]
+            if verbose:
+                cmd.insert(1, "-Xptxas")
+                cmd.insert(2, "-v")
+            result = subprocess.run(cmd, capture_output=True, text=True, check=False)
+            if result.returncode != 0:
+                scratch.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed:\n{result.stdout}\n{result.stderr}")
+            os.replace(scratch, LIBRARY)
+            if verbose:
+                print(result.stderr)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIBRARY
 
 
