@@ -53,8 +53,10 @@ enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 //                 1100 clocks per 128 x 256 tile)
 //   kStoreDirect: straight from registers, 32 bytes (one sector) per lane and store; touches no shared
 //                 memory, but the epilogue warps wait on the store path (a row per lane drains slowly)
-// Measured per shape (a third way, warps copying the staged tile out in 128-byte lines, never won):
-// TMA wins except where the main loop is long enough to hide the slower stores.
+// Measured per shape (a third way, warps copying the staged tile out in 128-byte lines, never won): in
+// short bursts direct stores win where the main loop is long (K >= 1536), but launched back to back
+// under the power cap the TMA store costs the least energy per launch for every shape, so it is the
+// default; LC0B200_GEMM_STORE selects the others for measurements.
 //   kStoreMixed : even groups staged and stored by TMA, odd groups straight from registers: half of each cost
 enum : int { kStoreTma = 0, kStoreMixed = 1, kStoreDirect = 2 };
 
@@ -1054,7 +1056,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   p.tma_store = tma_store ? 1 : 0;
   // Store mode of the grouped epilogue: see kStoreTma / kStoreDirect.
   const bool direct_ok = tma_store && (reinterpret_cast<uintptr_t>(g.out) & 31u) == 0 && (g.ldc % 16) == 0 && (g.n % 16) == 0;
-  int mode = (g.k >= 1536 && direct_ok) ? kStoreDirect : kStoreTma;
+  int mode = kStoreTma;  // the cheapest in energy per launch under the power cap for every shape measured
   const int forced = forced_store_mode();
   if (forced == kStoreTma || ((forced == kStoreDirect || forced == kStoreMixed) && direct_ok)) mode = forced;
   p.store_mode = mode;
