@@ -262,8 +262,9 @@ LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_pro
  * launch per graph node) for the graph of N:343-1550.  Shapes are the reference's layer sizes; weights
  * go in under the reference's canonical buffer names (every `name=` of N:343-1466, e.g.
  * "/encoder0/mha/Q/w/w") as bf16 in its input-major [K,N] layout, one-element constants
- * ("/encoder0/alpha*input/w", "/policy/scale/w", ...) included.  bf16 arithmetic, encoder LayerNorms
- * folded into the GEMM epilogues.  head depth (embedding / heads) must be 32.
+ * ("/encoder0/alpha*input/w", "/policy/scale/w", ...) included.  bf16 arithmetic with the encoder
+ * LayerNorms folded into the GEMM epilogues, or int8 GEMMs (config.int8_gemms).  head depth
+ * (embedding / heads) must be 32.
  *
  * All device memory is ONE caller-provided arena of lc0b200_net_arena_bytes() bytes (256-byte aligned):
  * weights as uploaded, the operands derived from them and the workspace for max_batch positions.
@@ -279,6 +280,9 @@ typedef struct lc0b200_net_config {
   int policy, policy_model;                           /* policy embedding and query/key widths */
   int value_embed, value_hidden, mlh_embed, mlh_hidden;
   float ln_eps;
+  int int8_gemms;  /* 0: bf16 throughout.  1: QKV, attention output and both FFN GEMMs of every encoder layer on
+                    * int8 operands (per-channel weight scales, per-token activation scales, s32 accumulation;
+                    * weights are quantised on the device in finalize) - no reference counterpart */
 } lc0b200_net_config;
 LC0B200_API size_t lc0b200_net_arena_bytes(const lc0b200_net_config* config, int max_batch); /* 0 = bad config */
 LC0B200_API int lc0b200_net_create(lc0b200_net** out, const lc0b200_net_config* config, int max_batch,

@@ -8,7 +8,9 @@
 // packed planes.  All device memory is one caller-provided arena; the object itself is a small host
 // structure.  The operator order is that of bt4/network.py (embedding :458-642, smolgen :778-849,
 // attention :1004-1076, FFN :1089-1186, policy :1261-1356, value / moves-left :1475-1550) with the
-// encoder LayerNorms deferred into the GEMM epilogues (see lc0b200_gemm_args); bf16 only.
+// encoder LayerNorms deferred into the GEMM epilogues (see lc0b200_gemm_args) in bf16 mode, or with the four
+// large GEMMs of every encoder layer on int8 operands and stand-alone LayerNorm kernels that also emit the
+// quantised rows (config.int8_gemms; no reference counterpart for that mode).
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -44,10 +46,13 @@ struct Dense {
   const void* bias = nullptr;
   const float* fold_c = nullptr;  // deferred LayerNorm: column sums of diag(gamma) W
   const float* fold_d = nullptr;  // beta^T W + bias
+  const float* col_scale = nullptr;  // int8 weights: per-output-channel scale (w then holds int8 [n, k])
 };
 
 struct Layer {
-  Dense compress_f, sg1, sg2, qkv_f, out, ffn1_f, ffn2;
+  Dense compress_f, sg1, sg2, qkv_f, out, ffn1_f, ffn2;  // bf16 mode (LayerNorms folded into *_f)
+  Dense compress, qkv, ffn1;                             // int8 mode (stand-alone LayerNorms); out / ffn2 shared
+  void* qkv_bias = nullptr;                              // int8 mode: Q, K, V biases back to back
 };
 
 // Bump allocator over the caller's arena; with base == nullptr it only measures.
@@ -89,6 +94,24 @@ __global__ void fold_layer_norm_kernel(__nv_bfloat16* __restrict__ packed, float
   d[col] = sum_d + (bias != nullptr ? __bfloat162float(bias[col]) : 0.0f);
 }
 
+// Symmetric per-output-channel int8 (the quantiser of the int8 GEMM path): s[n] = max_k |W[k,n]| / 127
+// (1 for an all-zero column), Wq[n,k] = clamp(rint(W[k,n] / s[n]), -127, 127), round-half-even, IEEE
+// division.  One thread per output column; upload-time only.
+__global__ void quantize_weight_kernel(int8_t* __restrict__ packed, float* __restrict__ scale,
+                                       const __nv_bfloat16* __restrict__ src, int k, int n) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  float amax = 0.0f;
+  for (int row = 0; row < k; ++row) amax = fmaxf(amax, fabsf(__bfloat162float(src[static_cast<long long>(row) * n + col])));
+  const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  scale[col] = s;
+  for (int row = 0; row < k; ++row) {
+    const float w = __bfloat162float(src[static_cast<long long>(row) * n + col]);
+    const int q = max(-127, min(127, __float2int_rn(__fdiv_rn(w, s))));
+    packed[static_cast<long long>(col) * k + row] = static_cast<int8_t>(q);
+  }
+}
+
 }  // namespace
 
 struct lc0b200_net {
@@ -107,6 +130,8 @@ struct lc0b200_net {
   void *pos_in, *position, *emb_in, *x[3], *branch, *hidden, *qkv, *merged, *compressed, *sg_hidden, *sg_gen, *sg_bias;
   void *pol_emb, *pol_q_buf, *pol_k_buf, *records, *val_emb, *val_hid, *mlh_emb, *mlh_hid;
   float* stats[3];
+  void *q_d = nullptr, *q_f = nullptr;  // int8 mode: quantised activations [t, embedding] and [t, ffn]
+  float* q_scale = nullptr;             // ... and their per-row scales
 };
 
 namespace {
@@ -215,14 +240,29 @@ void plan(lc0b200_net& net) {
   packed(net.emb_ffn2, d, f);
   packed(net.sg_shared, kSquares * kSquares, c.smolgen_gen);
   net.layers.assign(c.layers, Layer());
+  auto quantised = [&](Dense& dense, size_t n, size_t k) {
+    dense.n = static_cast<int>(n);
+    dense.k = static_cast<int>(k);
+    dense.w = a.take(n * k);
+    dense.col_scale = static_cast<float*>(a.take(n * 4));
+  };
   for (Layer& l : net.layers) {
-    folded(l.compress_f, c.smolgen_compress, d);
     packed(l.sg1, c.smolgen_hidden, static_cast<size_t>(kSquares) * c.smolgen_compress);
     packed(l.sg2, static_cast<size_t>(c.heads) * c.smolgen_gen, c.smolgen_hidden);
-    folded(l.qkv_f, 3 * d, d);
-    packed(l.out, d, d);
-    folded(l.ffn1_f, f, d);
-    packed(l.ffn2, d, f);
+    if (c.int8_gemms) {
+      packed(l.compress, c.smolgen_compress, d);
+      quantised(l.qkv, 3 * d, d);
+      l.qkv_bias = a.take(3 * d * 2);
+      quantised(l.out, d, d);
+      quantised(l.ffn1, f, d);
+      quantised(l.ffn2, d, f);
+    } else {
+      folded(l.compress_f, c.smolgen_compress, d);
+      folded(l.qkv_f, 3 * d, d);
+      packed(l.out, d, d);
+      folded(l.ffn1_f, f, d);
+      packed(l.ffn2, d, f);
+    }
   }
   packed(net.pol1, c.policy, d);
   packed(net.pol_q, c.policy_model, c.policy);
@@ -257,8 +297,14 @@ void plan(lc0b200_net& net) {
   net.val_hid = a.take(b * c.value_hidden * 2);
   net.mlh_emb = a.take(t * c.mlh_embed * 2);
   net.mlh_hid = a.take(b * c.mlh_hidden * 2);
-  const size_t parts = (d + 63) / 64;
-  for (auto& s : net.stats) s = static_cast<float*>(a.take(parts * t * 2 * 4));
+  if (c.int8_gemms) {
+    net.q_d = a.take(t * d);
+    net.q_f = a.take(t * f);
+    net.q_scale = static_cast<float*>(a.take(t * 4));
+  } else {
+    const size_t parts = (d + 63) / 64;
+    for (auto& s : net.stats) s = static_cast<float*>(a.take(parts * t * 2 * 4));
+  }
   a.take(0);
 }
 
@@ -269,20 +315,22 @@ const Slot* find(const lc0b200_net& net, const std::string& name) {
 
 // One GEMM through the public entry point (so that every argument check applies here too).
 int run_gemm(void* out, const void* a, const Dense& w, long long m, int activation, int out_kind, void* stream,
-             const void* bias_override = nullptr, bool use_bias = true) {
+             const void* bias_override = nullptr, bool use_bias = true, const float* row_scale = nullptr) {
   lc0b200_gemm_args g;
   std::memset(&g, 0, sizeof(g));
   g.out = out;
   g.a = a;
   g.w = w.w;
   g.bias_bf16 = bias_override != nullptr ? bias_override : (use_bias ? w.bias : nullptr);
+  g.row_scale = row_scale;
+  g.col_scale = w.col_scale;
   g.m = m;
   g.n = w.n;
   g.k = w.k;
   g.lda = w.k;
   g.ldw = w.k;
   g.ldc = w.n;
-  g.in_type = LC0B200_IN_BF16;
+  g.in_type = w.col_scale != nullptr ? LC0B200_IN_INT8 : LC0B200_IN_BF16;
   g.out_kind = out_kind;
   g.w_layout = LC0B200_W_NK;
   g.activation = activation;
@@ -446,6 +494,14 @@ LC0B200_API int lc0b200_net_finalize(lc0b200_net* net, void* stream) {
     }
     return cudaGetLastError() == cudaSuccess ? LC0B200_OK : LC0B200_ERR_CUDA;
   };
+  // int8 mode: `count` output channels of `weight` ([K, count] as uploaded) into rows [first, first + count)
+  // of the packed int8 operand, with their scales.
+  auto quantise = [&](Dense& dense, const std::string& weight, size_t first, size_t count) -> int {
+    quantize_weight_kernel<<<static_cast<unsigned>((count + 127) / 128), 128, 0, st>>>(
+        static_cast<int8_t*>(const_cast<void*>(dense.w)) + first * dense.k, const_cast<float*>(dense.col_scale) + first,
+        static_cast<const __nv_bfloat16*>(dev(weight)), dense.k, static_cast<int>(count));
+    return cudaGetLastError() == cudaSuccess ? LC0B200_OK : LC0B200_ERR_CUDA;
+  };
   NET_TRY(pack(net->pe, "/attn_body/embedding/preprocess/matmul/w", "/attn_body/embedding/preprocess/add/w"));
   NET_TRY(pack(net->emb, "/attn_body/matmul/w", nullptr));
   NET_TRY(pack(net->emb_ffn1, "/attn_body/ffn/dense1/w/w", "/attn_body/ffn/dense1/b/w"));
@@ -454,14 +510,33 @@ LC0B200_API int lc0b200_net_finalize(lc0b200_net* net, void* stream) {
   for (int i = 0; i < c.layers; ++i) {
     Layer& l = net->layers[i];
     const std::string prev = i == 0 ? std::string("/attn_body/ln2") : enc(i - 1, "/ln2");
-    NET_TRY(fold(l.compress_f, {enc(i, "/smolgen/compress/w")}, {}, prev));
     NET_TRY(pack(l.sg1, enc(i, "/smolgen/dense1/w/w"), nullptr));
     NET_TRY(pack(l.sg2, enc(i, "/smolgen/dense2/w/w"), nullptr));
-    NET_TRY(fold(l.qkv_f, {enc(i, "/mha/Q/w/w"), enc(i, "/mha/K/w/w"), enc(i, "/mha/V/w/w")},
-                 {enc(i, "/mha/Q/b/w"), enc(i, "/mha/K/b/w"), enc(i, "/mha/V/b/w")}, prev));
-    NET_TRY(pack(l.out, enc(i, "/mha/out/dense/w/w"), nullptr));
-    NET_TRY(fold(l.ffn1_f, {enc(i, "/ffn/dense1/w/w")}, {enc(i, "/ffn/dense1/b/w")}, enc(i, "/ln1")));
-    NET_TRY(pack(l.ffn2, enc(i, "/ffn/dense2/w/w"), nullptr));
+    if (c.int8_gemms) {
+      NET_TRY(pack(l.compress, enc(i, "/smolgen/compress/w"), nullptr));
+      const char* qkv_w[3] = {"/mha/Q/w/w", "/mha/K/w/w", "/mha/V/w/w"};
+      const char* qkv_b[3] = {"/mha/Q/b/w", "/mha/K/b/w", "/mha/V/b/w"};
+      const size_t d = c.embedding;
+      for (int part = 0; part < 3; ++part) {
+        NET_TRY(quantise(l.qkv, enc(i, qkv_w[part]), part * d, d));
+        if (cudaMemcpyAsync(static_cast<char*>(l.qkv_bias) + part * d * 2, dev(enc(i, qkv_b[part])), d * 2,
+                            cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
+          return LC0B200_ERR_CUDA;
+        }
+      }
+      l.qkv.bias = l.qkv_bias;
+      NET_TRY(quantise(l.out, enc(i, "/mha/out/dense/w/w"), 0, l.out.n));
+      NET_TRY(quantise(l.ffn1, enc(i, "/ffn/dense1/w/w"), 0, l.ffn1.n));
+      l.ffn1.bias = dev(enc(i, "/ffn/dense1/b/w"));
+      NET_TRY(quantise(l.ffn2, enc(i, "/ffn/dense2/w/w"), 0, l.ffn2.n));
+    } else {
+      NET_TRY(fold(l.compress_f, {enc(i, "/smolgen/compress/w")}, {}, prev));
+      NET_TRY(fold(l.qkv_f, {enc(i, "/mha/Q/w/w"), enc(i, "/mha/K/w/w"), enc(i, "/mha/V/w/w")},
+                   {enc(i, "/mha/Q/b/w"), enc(i, "/mha/K/b/w"), enc(i, "/mha/V/b/w")}, prev));
+      NET_TRY(pack(l.out, enc(i, "/mha/out/dense/w/w"), nullptr));
+      NET_TRY(fold(l.ffn1_f, {enc(i, "/ffn/dense1/w/w")}, {enc(i, "/ffn/dense1/b/w")}, enc(i, "/ln1")));
+      NET_TRY(pack(l.ffn2, enc(i, "/ffn/dense2/w/w"), nullptr));
+    }
   }
   NET_TRY(pack(net->pol1, "/policy/dense1/matmul/w", "/policy/dense1/add/w"));
   NET_TRY(pack(net->pol_q, "/policy/Q/matmul/w", "/policy/Q/add/w"));
@@ -532,6 +607,48 @@ LC0B200_API int lc0b200_net_forward(lc0b200_net* net, const uint64_t* masks, con
   NET_TRY(lc0b200_input_gating(skip, skip, dev("/ip_mul_gate/w"), dev("/ip_add_gate/w"), batch, kSquares, d, stream));
   NET_TRY(run_gemm(net->hidden, skip, net->emb_ffn1, t, LC0B200_ACT_MISH, LC0B200_OUT_BF16, stream));
 
+  void* body = nullptr;
+  if (c.int8_gemms) {
+    // ---- encoder tower, int8 GEMMs: stand-alone LayerNorm kernels that also emit the quantised rows
+    const float* qs = net->q_scale;
+    auto layer_norm_q = [&](void* out, const std::string& bias, const std::string& lnp, const void* skip_rows,
+                            const std::string& alpha) -> int {
+      return lc0b200_layer_norm(out, net->branch, dev(bias), skip_rows, dev(lnp + "/w/scale"), dev(lnp + "/w/bias"),
+                                dev(alpha), t, d, LC0B200_ACT_NONE, 1, eps, net->q_d, net->q_scale, stream);
+    };
+    NET_TRY(run_gemm(net->branch, net->hidden, net->emb_ffn2, t, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
+    body = net->x[1];
+    NET_TRY(layer_norm_q(body, "/attn_body/ffn/dense2/b/w", "/attn_body/ln2", skip, "/attn_body/ffn/alpha/w"));
+    void* spare[2] = {net->x[0], net->x[2]};
+    for (int i = 0; i < c.layers; ++i) {
+      const Layer& l = net->layers[i];
+      NET_TRY(run_gemm(net->qkv, net->q_d, l.qkv, t, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream, nullptr, true, qs));
+      NET_TRY(run_gemm(net->compressed, body, l.compress, t, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
+      NET_TRY(run_gemm(net->sg_hidden, net->compressed, l.sg1, b, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
+      NET_TRY(lc0b200_layer_norm(net->sg_hidden, net->sg_hidden, dev(enc(i, "/smolgen/dense1/b/w")), nullptr,
+                                 dev(enc(i, "/smolgen/ln1/w/scale")), dev(enc(i, "/smolgen/ln1/w/bias")), nullptr, b,
+                                 c.smolgen_hidden, LC0B200_ACT_SWISH, 0, eps, nullptr, nullptr, stream));
+      NET_TRY(run_gemm(net->sg_gen, net->sg_hidden, l.sg2, b, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
+      NET_TRY(lc0b200_layer_norm(net->sg_gen, net->sg_gen, dev(enc(i, "/smolgen/dense2/b/w")), nullptr,
+                                 dev(enc(i, "/smolgen/ln2/w/scale")), dev(enc(i, "/smolgen/ln2/w/bias")), nullptr, b,
+                                 h * c.smolgen_gen, LC0B200_ACT_SWISH, 0, eps, nullptr, nullptr, stream));
+      NET_TRY(run_gemm(net->sg_bias, net->sg_gen, net->sg_shared, b * h, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
+      NET_TRY(lc0b200_attention(net->merged, net->qkv, bf(net->qkv, d), bf(net->qkv, 2 * d), net->sg_bias,
+                                scalar(enc(i, "/mha/QK/scale/w")), b, h, 32, 3LL * d, 3LL * d, 3LL * d, d, stream));
+      NET_TRY(lc0b200_quantize_rows(net->q_d, net->q_scale, net->merged, t, d, d, stream));
+      NET_TRY(run_gemm(net->branch, net->q_d, l.out, t, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream, nullptr, false, qs));
+      void* attended = spare[0];
+      NET_TRY(layer_norm_q(attended, enc(i, "/mha/out/dense/b/w"), enc(i, "/ln1"), body, enc(i, "/alpha*input/w")));
+      NET_TRY(run_gemm(net->hidden, net->q_d, l.ffn1, t, LC0B200_ACT_MISH, LC0B200_OUT_BF16, stream, nullptr, true, qs));
+      NET_TRY(lc0b200_quantize_rows(net->q_f, net->q_scale, net->hidden, t, c.ffn, c.ffn, stream));
+      NET_TRY(run_gemm(net->branch, net->q_f, l.ffn2, t, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream, nullptr, false, qs));
+      void* next = spare[1];
+      NET_TRY(layer_norm_q(next, enc(i, "/ffn/dense2/b/w"), enc(i, "/ln2"), attended, enc(i, "/ffn/alpha/w")));
+      spare[0] = body;
+      spare[1] = attended;
+      body = next;
+    }
+  } else {
   // ---- encoder tower with the LayerNorms deferred into the GEMM epilogues
   void* z = net->x[1];
   float* stats = net->stats[0];
@@ -576,9 +693,10 @@ LC0B200_API int lc0b200_net_forward(lc0b200_net* net, const uint64_t* masks, con
     stats = stats2;
     ln = enc(i, "/ln2");
   }
-  void* body = free_z[0];
+  body = free_z[0];
   NET_TRY(lc0b200_layer_norm(body, z, net->zero_bias, nullptr, dev(ln + "/w/scale"), dev(ln + "/w/bias"), nullptr, t, d,
                              LC0B200_ACT_NONE, 0, eps, nullptr, nullptr, stream));
+  }
 
   // ---- policy head (network.py:1261-1356)
   NET_TRY(run_gemm(net->pol_emb, body, net->pol1, t, LC0B200_ACT_MISH, LC0B200_OUT_BF16, stream));

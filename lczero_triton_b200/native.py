@@ -23,20 +23,24 @@ class NetConfigC(ctypes.Structure):
 
     _fields_ = [(name, ctypes.c_int) for name in (
         "embedding", "layers", "heads", "ffn", "pos_enc", "smolgen_compress", "smolgen_hidden", "smolgen_gen",
-        "policy", "policy_model", "value_embed", "value_hidden", "mlh_embed", "mlh_hidden")] + [("ln_eps", ctypes.c_float)]
+        "policy", "policy_model", "value_embed", "value_hidden", "mlh_embed", "mlh_hidden")] + [
+            ("ln_eps", ctypes.c_float), ("int8_gemms", ctypes.c_int)]
 
     @classmethod
-    def from_config(cls, cfg: NetConfig) -> "NetConfigC":
+    def from_config(cls, cfg: NetConfig, mode: str = "bf16") -> "NetConfigC":
         return cls(cfg.embedding, cfg.layers, cfg.heads, cfg.ffn, cfg.pos_enc, cfg.smolgen_compress, cfg.smolgen_hidden,
                    cfg.smolgen_gen, cfg.policy, cfg.policy_model, cfg.value_embed, cfg.value_hidden, cfg.mlh_embed,
-                   cfg.mlh_hidden, cfg.ln_eps)
+                   cfg.mlh_hidden, cfg.ln_eps, 1 if mode == "int8" else 0)
 
 
 class NativeNet:
-    """A BT4-style network held by the C library (bf16, LayerNorms folded into the GEMMs)."""
+    """A BT4-style network held by the C library: bf16 with the LayerNorms folded into the GEMMs, or
+    (``mode="int8"``) int8 GEMMs with stand-alone LayerNorm kernels."""
 
     def __init__(self, weights: Mapping[str, torch.Tensor], config: NetConfig, max_batch: int, *,
-                 device: str | torch.device = "cuda") -> None:
+                 device: str | torch.device = "cuda", mode: str = "bf16") -> None:
+        if mode not in ("bf16", "int8"):
+            raise ValueError("mode must be 'bf16' or 'int8'")
         self._lib = _lib.load()
         self._handle = ctypes.c_void_p()
         self.cfg = config
@@ -44,7 +48,7 @@ class NativeNet:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise ValueError("NativeNet needs a CUDA device; there is no CPU path")
-        cfg_c = NetConfigC.from_config(config)
+        cfg_c = NetConfigC.from_config(config, mode)
         nbytes = self._lib.lc0b200_net_arena_bytes(ctypes.byref(cfg_c), max_batch)
         if nbytes == 0:
             raise ValueError("the C library rejects this network shape (head depth must be 32)")

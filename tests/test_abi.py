@@ -83,7 +83,7 @@ C_CALLER = r"""
 #include <stdio.h>
 #include "lc0b200.h"
 int main(void) {
-  lc0b200_net_config cfg = {128, 4, 4, 256, 64, 16, 64, 64, 128, 128, 128, 128, 32, 128, 1e-3f};
+  lc0b200_net_config cfg = {128, 4, 4, 256, 64, 16, 64, 64, 128, 128, 128, 128, 32, 128, 1e-3f, 0};
   size_t bytes = lc0b200_net_arena_bytes(&cfg, 32);
   lc0b200_gemm_args args = {0};
   printf("%zu %d %d %s\n", bytes, lc0b200_gemm(&args, NULL),

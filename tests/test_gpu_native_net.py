@@ -84,6 +84,25 @@ def test_bt4_shape_through_the_c_object_matches_the_python_network(pkg) -> None:
     native.close()
 
 
+@pytest.mark.parametrize("name", ["TINY", "BT4"])
+def test_int8_mode_through_the_c_object_equals_the_python_network(pkg, name) -> None:
+    """int8 GEMMs, stand-alone LayerNorms: nothing is summed differently on the two sides (the weights
+    are quantised by the same rule, on the device here and on the host there), so the outputs agree
+    bit for bit."""
+    cfg = getattr(pkg["config"], name)
+    batch = 6
+    weights = pkg["weights"].random_weights(cfg, 2)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, 2)
+    native = pkg["native"].NativeNet(weights, cfg, max_batch=8, mode="int8")
+    got = [x.cpu() for x in native.forward(masks.cuda(), values.cuda())]
+    _no_timeouts(pkg)
+    ref = pkg["net"].Bt4Net(weights, cfg, mode="int8")
+    want = [x.cpu() for x in ref.forward(masks.cuda(), values.cuda())]
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    native.close()
+
+
 def test_object_rejects_misuse(pkg) -> None:
     lib = pkg["lib"].load()
     cfg = pkg["config"].TINY
