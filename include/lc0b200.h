@@ -200,6 +200,14 @@ LC0B200_API int lc0b200_attention(void* out_bf16, const void* q_bf16, const void
  * s = max|x| / 127 (1 if the row is all zero), q = clamp(rint(x / s), -127, 127), round-half-even. */
 LC0B200_API int lc0b200_quantize_rows(void* out_int8, float* scale_f32, const void* in_bf16, long long row_count,
                           int width, long long ld_in, void* stream);
+/* Rows of a deferred LayerNorm straight to per-row int8 (no reference counterpart): with mean / rstd of
+ * row m from the partial sums stats[parts][row_count][2] that lc0b200_gemm wrote (stats_out) over a width
+ * of `width`, y = bf16((z - mean) * rstd * gamma + beta), then quantised as lc0b200_quantize_rows does.
+ * width a multiple of 8, at most 2048; pointers 16-byte aligned. */
+LC0B200_API int lc0b200_normalize_quantize_rows(void* out_int8, float* scale_f32, const void* z_bf16,
+                                                const float* stats, int parts, const void* gamma_bf16,
+                                                const void* beta_bf16, long long row_count, int width, float epsilon,
+                                                void* stream);
 /* One int8 dense layer on bf16 activations (no reference counterpart): quantise the rows of a
  * (lc0b200_quantize_rows) into caller-provided scratch, then out = act(dequant(Aq @ Wq) + bias)
  * (lc0b200_gemm with int8 inputs).  w_nk_int8 is [n,k] row-major, col_scale the per-output-channel

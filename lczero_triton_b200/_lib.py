@@ -63,6 +63,7 @@ SIGNATURES: dict[str, tuple] = {
     "lc0b200_softmax_64": (_P, _P, _P, _L, _P),
     "lc0b200_attention": (_P, _P, _P, _P, _P, _F, _L, _I, _I, _L, _L, _L, _L, _P),
     "lc0b200_quantize_rows": (_P, _P, _P, _L, _I, _L, _P),
+    "lc0b200_normalize_quantize_rows": (_P, _P, _P, _P, _I, _P, _P, _L, _I, _F, _P),
     "lc0b200_linear_int8": (_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _P),
     "lc0b200_linear_int8_static": (_P, _P, _P, _P, _P, _L, _I, _I, _I, _P),
     "lc0b200_promotion_logits": (_P, _P, _P, _I, _I, _P),

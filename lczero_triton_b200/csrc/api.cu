@@ -306,6 +306,14 @@ LC0B200_API int lc0b200_quantize_rows(void* out, float* scale, const void* in, l
   return quantize_rows(out, scale, in, row_count, width, ld_in, S(stream));
 }
 
+LC0B200_API int lc0b200_normalize_quantize_rows(void* out, float* scale, const void* z, const float* stats, int parts,
+                                                const void* gamma, const void* beta, long long row_count, int width,
+                                                float epsilon, void* stream) {
+  REQUIRE_PTR(out); REQUIRE_PTR(scale); REQUIRE_PTR(z); REQUIRE_PTR(stats); REQUIRE_PTR(gamma); REQUIRE_PTR(beta);
+  REQUIRE_SHAPE(row_count >= 0 && width > 0 && parts > 0 && epsilon > 0.0f && row_count <= 8LL * 0x7FFFFFFF);
+  return normalize_quantize_rows(out, scale, z, stats, parts, gamma, beta, row_count, width, epsilon, S(stream));
+}
+
 LC0B200_API int lc0b200_linear_int8(void* out, const void* a, const void* w_nk, const float* col_scale,
                                     const void* bias, void* scratch_q, float* scratch_scale, long long m, int n,
                                     int k, int activation, void* stream) {

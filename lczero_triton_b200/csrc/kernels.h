@@ -34,6 +34,8 @@ int linear_int8(void* out, const void* a, const void* w_nk, const float* col_sca
                 cudaStream_t stream);
 
 // layernorm.cu
+int normalize_quantize_rows(void* q_out, float* q_scale, const void* z, const float* stats, int parts, const void* gamma,
+                            const void* beta, long long rows, int width, float epsilon, cudaStream_t st);
 int layer_norm(void* out, const void* in, const void* bias, const void* skip, const void* gamma, const void* beta,
                const void* alpha, long long rows, int width, int activation, int has_skip, float epsilon,
                void* q_out, float* q_scale, cudaStream_t st);

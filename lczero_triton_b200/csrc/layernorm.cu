@@ -290,6 +290,99 @@ int launch_warp(const LnParams& p, cudaStream_t st) {
   return launch_status();
 }
 
+// Deferred-LayerNorm rows straight to per-row int8: y = (z - mean) * rstd * gamma + beta with mean / rstd
+// from the partial row sums a residual GEMM wrote (lc0b200_gemm_args::stats_out), rounded to bf16 (what a
+// LayerNorm kernel would have stored), then s = max|y| / 127, q = rint(y * (127 / max|y|)).  One warp per
+// row, the row in registers between the two passes; nothing but z is read at full width.
+template <int GROUPS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+normalize_quantize_kernel(int8_t* __restrict__ q_out, float* __restrict__ q_scale, const bf16* __restrict__ z,
+                          const float2* __restrict__ stats, int parts, const bf16* __restrict__ gamma,
+                          const bf16* __restrict__ beta, long long rows, int width, float epsilon) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * static_cast<long long>(kWarpsPerBlock) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  // mean and 1/sqrt(var + eps) from the partials (lanes share the loads, a shuffle sums them)
+  float s = 0.0f, q = 0.0f;
+  for (int i = lane; i < parts; i += 32) {
+    const float2 t = __ldg(stats + static_cast<long long>(i) * rows + row);
+    s += t.x;
+    q += t.y;
+  }
+  s = warp_sum(s);
+  q = warp_sum(q);
+  const float inv_width = 1.0f / static_cast<float>(width);
+  const float mean = s * inv_width;
+  const float rstd = rsqrtf(fmaxf(q * inv_width - mean * mean, 0.0f) + epsilon);
+  const float shift = -mean * rstd;
+  const int groups = width >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(z + row * width);
+  float y[GROUPS][8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = lane + 32 * g;
+    if (idx < groups) {
+      float v[8], ga[8], be[8];
+      unpack8(__ldg(src + idx), v);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + idx), ga);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(beta) + idx), be);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y0 = fmaf(fmaf(v[2 * j], rstd, shift), ga[2 * j], be[2 * j]);
+        const float y1 = fmaf(fmaf(v[2 * j + 1], rstd, shift), ga[2 * j + 1], be[2 * j + 1]);
+        const float2 r = unpack_bf16x2(pack_bf16x2(y0, y1));  // the quantiser sees bf16 values
+        y[g][2 * j] = r.x;
+        y[g][2 * j + 1] = r.y;
+        amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 1.0f;
+  if (lane == 0) q_scale[row] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(q_out + row * width);
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = lane + 32 * g;
+    if (idx < groups) {
+      uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int qv = max(-127, min(127, __float2int_rn(y[g][j] * inv)));
+        packed[j >> 2] |= static_cast<uint32_t>(qv & 0xFF) << ((j & 3) * 8);
+      }
+      dst[idx] = make_uint2(packed[0], packed[1]);
+    }
+  }
+}
+
+}  // namespace
+
+int normalize_quantize_rows(void* q_out, float* q_scale, const void* z, const float* stats, int parts, const void* gamma,
+                            const void* beta, long long rows, int width, float epsilon, cudaStream_t st) {
+  if (rows == 0) return LC0B200_OK;
+  if ((width % 8) != 0 || width > 256 * kMaxGroups) return LC0B200_ERR_UNSUPPORTED;
+  if (!aligned16(q_out) || !aligned16(z) || !aligned16(gamma) || !aligned16(beta) || (reinterpret_cast<uintptr_t>(stats) & 7u)) {
+    return LC0B200_ERR_MISALIGNED;
+  }
+  const unsigned blocks = static_cast<unsigned>(ceil_div_ll(rows, kWarpsPerBlock));
+  const dim3 block(kWarpsPerBlock * 32);
+  auto* qo = reinterpret_cast<int8_t*>(q_out);
+  const auto* zz = reinterpret_cast<const bf16*>(z);
+  const auto* st2 = reinterpret_cast<const float2*>(stats);
+  const auto* ga = reinterpret_cast<const bf16*>(gamma);
+  const auto* be = reinterpret_cast<const bf16*>(beta);
+  const int g = (width + 255) / 256;
+  if (g <= 1) normalize_quantize_kernel<1><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else if (g <= 2) normalize_quantize_kernel<2><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else if (g <= 4) normalize_quantize_kernel<4><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else normalize_quantize_kernel<8><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  return launch_status();
+}
+
+namespace {
 }  // namespace
 
 int layer_norm(void* out, const void* in, const void* bias, const void* skip, const void* gamma, const void* beta,

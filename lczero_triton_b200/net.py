@@ -320,10 +320,10 @@ class Bt4Net:
             return ops.layer_norm(out, z, self.zero_bias, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], row_count=t, width=d,
                                   epsilon=eps)
 
-        def normalise_and_quantise(z: torch.Tensor, ln: str) -> None:
-            """int8 mode: LayerNorm(z) straight to per-row int8 (no bf16 copy is stored)."""
-            ops.layer_norm(None, z, self.zero_bias, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], row_count=t, width=d,
-                           epsilon=eps, q_out=qd, q_scale=qs)
+        def normalise_and_quantise(z: torch.Tensor, ln: str, row_stats: torch.Tensor) -> None:
+            """int8 mode: LayerNorm(z) straight to per-row int8 (no bf16 copy is stored), mean and variance
+            from the partial sums the producing GEMM wrote."""
+            ops.normalize_quantize_rows(qd, qs, z, row_stats, w[f"{ln}/w/scale"], w[f"{ln}/w/bias"], t, d, eps)
 
         # embedding FFN tail: z = alpha * (hidden @ W2 + b2) + skip   (skip is a plain tensor here)
         z, stats, ln = ws["x1"], ws["stats0"], "/attn_body/ln2"
@@ -337,7 +337,7 @@ class Bt4Net:
         for i, layer in enumerate(self.layers):
             p = f"/encoder{i}"
             if q8:
-                normalise_and_quantise(z, ln)
+                normalise_and_quantise(z, ln, stats)
                 self._gemm(ws["qkv"], qd, layer["qkv"], t, row_scale=qs)
             else:
                 self._gemm_folded(ws["qkv"], z, layer["qkv_f"], t, stats)
@@ -354,7 +354,7 @@ class Bt4Net:
                      res_alpha=self._scalars[f"{p}/alpha*input/w"], stats_out=stats1, ln_eps=eps)
             a_ffn2, scale_ffn2 = ws["hidden"], None
             if q8:
-                normalise_and_quantise(z1, f"{p}/ln1")
+                normalise_and_quantise(z1, f"{p}/ln1", stats1)
                 self._gemm(ws["hidden"], qd, layer["ffn1"], t, activation="mish", row_scale=qs)
                 ops.quantize_rows(qf, qs, ws["hidden"], t, c.ffn)
                 a_ffn2, scale_ffn2 = qf, qs

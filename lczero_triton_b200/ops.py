@@ -200,6 +200,18 @@ def quantize_rows(out: torch.Tensor, scale: torch.Tensor, x: torch.Tensor, row_c
     return out, scale
 
 
+def normalize_quantize_rows(out: torch.Tensor, scale: torch.Tensor, z: torch.Tensor, stats: torch.Tensor,
+                            gammas: torch.Tensor, betas: torch.Tensor, row_count: int, width: int,
+                            epsilon: float = 1e-3) -> tuple[torch.Tensor, torch.Tensor]:
+    """Deferred-LayerNorm rows (``z`` with the partial sums ``stats [parts, rows, 2]`` of a residual GEMM)
+    normalised, rounded to bf16 and quantised per row to int8."""
+    _require(out, torch.int8, "out"); _require(scale, torch.float32, "scale"); _require(z, torch.bfloat16, "z")
+    check(_lib.load().lc0b200_normalize_quantize_rows(_p(out), _p(scale), _p(z), _p(stats), stats.shape[0], _p(gammas),
+                                                      _p(betas), row_count, width, epsilon, _stream()),
+          "normalize_quantize_rows")
+    return out, scale
+
+
 def linear_int8(out: torch.Tensor, a: torch.Tensor, w_nk: torch.Tensor, col_scale: torch.Tensor,
                 bias: torch.Tensor | None, scratch_q: torch.Tensor, scratch_scale: torch.Tensor, *, m: int, n: int,
                 k: int, activation: str = "none") -> torch.Tensor:

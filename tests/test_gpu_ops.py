@@ -239,6 +239,31 @@ def test_quantize_rows_is_bit_exact(ops, rows, width) -> None:
     assert s[0] == 1 and q[0].abs().sum() == 0
 
 
+@pytest.mark.parametrize(("rows", "width"), [(300, 1024), (77, 768), (9, 2048), (5, 64)])
+def test_normalize_quantize_rows_from_partial_sums(ops, rows, width) -> None:
+    """Deferred-LayerNorm rows to int8: mean / variance come from the 64-column partial sums a residual GEMM
+    writes; the result must be the quantisation of the bf16-rounded LayerNorm (layer_norm.py:57-87 semantics)."""
+    from oracle import int8_oracle
+
+    z = _bf(torch.randn((rows, width), generator=_gen(56)) * 1.5 + 0.1)
+    gamma = _bf(1.0 + 0.1 * torch.randn(width, generator=_gen(57)))
+    beta = _bf(0.1 * torch.randn(width, generator=_gen(58)))
+    groups = z.float().reshape(rows, width // 64, 64)
+    stats = torch.stack((groups.sum(dim=2), (groups * groups).sum(dim=2)), dim=2).permute(1, 0, 2).contiguous()
+    q = torch.empty((rows, width), dtype=torch.int8, device="cuda")
+    s = torch.empty((rows,), dtype=torch.float32, device="cuda")
+    ops.normalize_quantize_rows(q, s, _dev(z), stats.cuda(), _dev(gamma), _dev(beta), rows, width, 1e-3)
+    zf = z.double()
+    mean = zf.mean(dim=1, keepdim=True)
+    var = (zf * zf).mean(dim=1, keepdim=True) - mean * mean
+    y = ((zf - mean) / torch.sqrt(var + 1e-3) * gamma.double() + beta.double()).float().to(torch.bfloat16)
+    want_q, want_s = int8_oracle.quantize_rows(y)
+    # fp32 against fp64 statistics: a bf16 rounding may flip here and there, never more than one step
+    torch.testing.assert_close(s.cpu(), want_s, rtol=1e-2, atol=0)
+    diff = (q.cpu().int() - want_q.int()).abs()
+    assert int(diff.max()) <= 1 and float((diff == 0).float().mean()) > 0.995
+
+
 # ------------------------------------------------------------------ softmax and attention
 
 def test_softmax_random_rows(ops, golden) -> None:
