@@ -425,6 +425,30 @@ def run_kernel(args) -> None:
                      "out": args.out, "ms": ms, "achieved": achieved, "unit": "TFLOP/s", "peak": peak,
                      "frac": achieved / peak, "peak_source": "measured burst int8 (library GEMM 8192^3)" if int8 else f"{peak_kind} burst bf16",
                      "algorithmic_bytes": m * k * eb + n * k * eb + m * n * out.element_size()})
+    elif args.kernel in ("quantize", "normalize_quantize"):
+        # int8 row quantisers: bf16 rows in, int8 rows and one f32 scale per row out
+        rows, width = args.rows, args.width
+        x = torch.randn((rows, width), generator=gen, device="cuda").to(torch.bfloat16)
+        q = torch.empty((rows, width), dtype=torch.int8, device="cuda")
+        sc = torch.empty((rows,), dtype=torch.float32, device="cuda")
+        if args.kernel == "quantize":
+            def once() -> None:
+                ops.quantize_rows(q, sc, x, rows, width)
+            nbytes = rows * (width * 3.0 + 4.0)
+        else:
+            groups = x.float().reshape(rows, width // 64, 64)
+            stats = torch.stack((groups.sum(dim=2), (groups * groups).sum(dim=2)), dim=2).permute(1, 0, 2).contiguous()
+            gamma = (1.0 + 0.1 * torch.randn(width, generator=gen, device="cuda")).to(torch.bfloat16)
+            beta = (0.1 * torch.randn(width, generator=gen, device="cuda")).to(torch.bfloat16)
+
+            def once() -> None:
+                ops.normalize_quantize_rows(q, sc, x, stats, gamma, beta, rows, width)
+            nbytes = rows * (width * 3.0 + 4.0 + (width // 64) * 8.0)
+        ms = _timed_steps(once, 3, args.iters, None) / args.iters
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        line.update({"rows": rows, "width": width, "ms": ms, "achieved": achieved, "unit": "GB/s",
+                     "peak": peaks["hbm_gbs"], "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy",
+                     "algorithmic_bytes": nbytes})
     elif args.kernel == "attention":
         b, h, d = args.batch, 32, 1024
         q, k_, v = (torch.randn((b, 64, d), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(3))
@@ -476,7 +500,7 @@ def main() -> None:
     ap.add_argument("--graph", type=int, default=1, help="replay the forward from a CUDA graph in the timed loop")
     ap.add_argument("--deferred-ln", type=int, default=-1,
                     help="LayerNorm folded into the GEMM epilogues: 1 / 0, or -1 for the mode's default")
-    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm"],
+    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm", "quantize", "normalize_quantize"],
                     help="measure one kernel instead of the whole forward pass")
     ap.add_argument("--m", type=int, default=262144)
     ap.add_argument("--n", type=int, default=3072)

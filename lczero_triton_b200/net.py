@@ -72,11 +72,12 @@ class Bt4Net:
             raise ValueError("Bt4Net needs a CUDA device; there is no CPU path")
         if self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
-        # bf16 mode keeps the residual stream un-normalised between GEMMs ("deferred LayerNorm"): the
-        # two LayerNorm launches per encoder layer become epilogue arithmetic (see lc0b200_gemm_args).
-        # (Available for int8 too, but there the short int8 main loop cannot hide the heavier epilogue
-        # and the stand-alone LayerNorm path measures faster, so it is off by default.)
-        self.deferred = (mode == "bf16") if deferred_layer_norm is None else bool(deferred_layer_norm)
+        # The residual stream is kept un-normalised between GEMMs ("deferred LayerNorm"): the two
+        # LayerNorm launches per encoder layer become epilogue arithmetic (see lc0b200_gemm_args).  In
+        # int8 mode the GEMMs that read the stream need quantised rows, which one light kernel makes
+        # from the un-normalised rows and the partial sums (ops.normalize_quantize_rows); measured 2 %
+        # faster than stand-alone LayerNorm kernels that also emit the int8 rows.
+        self.deferred = True if deferred_layer_norm is None else bool(deferred_layer_norm)
         self._layout = _lib.W_NK if weight_layout == "nk" else _lib.W_KN
         self._w = {k: v.to(device=self.device, dtype=torch.bfloat16).contiguous() for k, v in weights.items()}
         self._scalars = {k: float(v.float().reshape(-1)[0]) for k, v in weights.items() if v.numel() == 1}
