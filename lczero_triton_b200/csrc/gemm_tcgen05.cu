@@ -9,17 +9,18 @@
 // its own 128 rows of A and its own half of the weight tile, the leader CTA issues MMAs that read
 // both shared memories, each CTA's TMEM receives its 128 rows of the accumulator).  No load is
 // multicast: every CTA fetches its own operands with plain per-CTA TMA.  Warp roles:
-//   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
-//   warp 1      MMA issuer     (one elected lane issues tcgen05.mma; owns the TMEM allocation)
+//   warp 0      TMA producer   (the whole warp follows the loop, one elected lane issues the
+//                               cp.async.bulk.tensor loads)
+//   warp 1      MMA issuer     (likewise; one elected lane issues tcgen05.mma; owns the TMEM allocation)
 //   warps 2..   epilogue       (eight warps for BN >= 128: two per TMEM lane quarter, each taking
 //                               half of the tile's columns in groups of 64)
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1.  The epilogue is organised so that nothing it needs from global memory is
 // on the critical path after the accumulator arrives: per-row LayerNorm statistics are read while
-// the tile is still being multiplied, the residual operand of a 32 x 64 group is brought into the
-// warp's swizzled staging buffer by TMA ahead of time, the result overwrites it in place and the warp
-// copies the buffer out in full 128-byte lines (a TMA store of the buffer when the row length does
-// not allow 16-byte pieces: TMA stores were measured to hold up the operand loads of the main loop).
+// the tile is still being multiplied, the per-column vectors of the tile wait in shared memory (put
+// there one tile ahead), the residual operand of a 32 x 64 group is brought into the warp's swizzled
+// staging buffer by TMA ahead of time, the result overwrites it in place and leaves by TMA store.  The
+// accumulator goes back to the MMA warp as soon as its last columns are in registers.
 // f32 / raw s32 results, narrow tiles and unaligned outputs use direct stores.  Operands are staged
 // K-major with the 128-byte swizzle; the weight operand may instead be staged MN-major straight from
 // the reference's [K,N] layout.
@@ -57,7 +58,7 @@ enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 // short bursts direct stores win where the main loop is long (K >= 1536), but launched back to back
 // under the power cap the TMA store costs the least energy per launch for every shape, so it is the
 // default; LC0B200_GEMM_STORE selects the others for measurements.
-//   kStoreMixed : even groups staged and stored by TMA, odd groups straight from registers: half of each cost
+//   kStoreMixed : even groups staged and stored by TMA, odd groups straight from registers (half of each cost)
 enum : int { kStoreTma = 0, kStoreMixed = 1, kStoreDirect = 2 };
 
 template <int BN, int CTAS, int MODE>
