@@ -60,6 +60,20 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
   return __bfloat1622float2(b);
 }
 
+// Four values times `inv`, rounded half-to-even and packed as int8 (low byte first).  The saturating
+// conversion clamps to [-128, 127]; callers pass inv = 127 / max|x|, so that |x * inv| <= 127 and the
+// result lies in [-127, 127] as the symmetric quantiser defines it.
+__device__ __forceinline__ uint32_t quantize4_s8(float a, float b, float c, float d, float inv) {
+  int q0, q1, q2, q3;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(a * inv));
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(b * inv));
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q2) : "f"(c * inv));
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q3) : "f"(d * inv));
+  const uint32_t lo = __byte_perm(static_cast<uint32_t>(q0), static_cast<uint32_t>(q1), 0x0040);
+  const uint32_t hi = __byte_perm(static_cast<uint32_t>(q2), static_cast<uint32_t>(q3), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
 __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -230,16 +230,8 @@ __global__ void __launch_bounds__(kBlock) embed_concat_kernel(bf16* __restrict__
 // s = max|x| / 127 (1 when the row is all zero); q = clamp(rint(x * (127 / max|x|)), -127, 127).
 // Rows up to 2048 wide stay in registers between the two passes.
 __device__ __forceinline__ uint2 quantize8(const uint4& raw, float inv) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = unpack_bf16x2(w[j]);
-    const int q0 = max(-127, min(127, __float2int_rn(f.x * inv)));
-    const int q1 = max(-127, min(127, __float2int_rn(f.y * inv)));
-    packed[j >> 1] |= (static_cast<uint32_t>(q0 & 0xFF) | (static_cast<uint32_t>(q1 & 0xFF) << 8)) << ((j & 1) * 16);
-  }
-  return make_uint2(packed[0], packed[1]);
+  const float2 f0 = unpack_bf16x2(raw.x), f1 = unpack_bf16x2(raw.y), f2 = unpack_bf16x2(raw.z), f3 = unpack_bf16x2(raw.w);
+  return make_uint2(quantize4_s8(f0.x, f0.y, f1.x, f1.y, inv), quantize4_s8(f2.x, f2.y, f3.x, f3.y, inv));
 }
 
 __device__ __forceinline__ float amax8(const uint4& raw, float amax) {

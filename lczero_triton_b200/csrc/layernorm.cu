@@ -142,13 +142,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(co
     for (int g = 0; g < GROUPS; ++g) {
       const int idx = lane + 32 * g;
       if (idx < groups) {
-        uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int q = max(-127, min(127, __float2int_rn(v[g][j] * inv)));
-          packed[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << ((j & 3) * 8);
-        }
-        qdst[idx] = make_uint2(packed[0], packed[1]);
+        qdst[idx] = make_uint2(quantize4_s8(v[g][0], v[g][1], v[g][2], v[g][3], inv),
+                               quantize4_s8(v[g][4], v[g][5], v[g][6], v[g][7], inv));
       }
     }
   }
@@ -354,13 +349,8 @@ normalize_quantize_kernel(int8_t* __restrict__ q_out, float* __restrict__ q_scal
   for (int g = 0; g < GROUPS; ++g) {
     const int idx = lane + 32 * g;
     if (idx < groups) {
-      uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int qv = max(-127, min(127, __float2int_rn(y[g][j] * inv)));
-        packed[j >> 2] |= static_cast<uint32_t>(qv & 0xFF) << ((j & 3) * 8);
-      }
-      dst[idx] = make_uint2(packed[0], packed[1]);
+      dst[idx] = make_uint2(quantize4_s8(y[g][0], y[g][1], y[g][2], y[g][3], inv),
+                            quantize4_s8(y[g][4], y[g][5], y[g][6], y[g][7], inv));
     }
   }
 }
