@@ -234,7 +234,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       // scores * scale + bias, clamp, row max
       float v[64];
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
       const uint32_t bias_row = stage_base + s * kStageBytes + kOffBias + e * kTileBias + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -252,19 +252,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int j = 0; j < 8; ++j) {
           const float x = clamp_keep_nan(fmaf(__uint_as_float(sraw[c * 8 + j]), p.scale, b[j]));
           v[c * 8 + j] = x;
-          mx = fmaxf(mx, x);
+          mx4[j & 3] = fmaxf(mx4[j & 3], x);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float off = mx * kLog2e;
-      float sum = 0.0f;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint32_t pk[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float p0 = fast_exp2(fmaf(v[2 * j], kLog2e, -off));
         const float p1 = fast_exp2(fmaf(v[2 * j + 1], kLog2e, -off));
-        sum += p0 + p1;
+        sum4[j & 3] += p0 + p1;
         pk[j] = pack_bf16x2(p0, p1);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // P row into the K-major, 128-byte-swizzled A operand of the second product: K block e.
       ok = ptx::mbar_wait(bar_p_empty + 8 * t, ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x670u + t);
       if (!ok) break;
