@@ -235,7 +235,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // scores * scale + bias, clamp, row max
       float v[64];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
-      float mn4[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
       const uint32_t bias_row = stage_base + s * kStageBytes + kOffBias + e * kTileBias + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -254,15 +253,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const float x = fmaf(__uint_as_float(sraw[c * 8 + j]), p.scale, b[j]);
           v[c * 8 + j] = x;
           mx4[j & 3] = fmaxf(mx4[j & 3], x);
-          mn4[j & 3] = fminf(mn4[j & 3], x);
         }
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float mn = fminf(fminf(mn4[0], mn4[1]), fminf(mn4[2], mn4[3]));
-      // The reference clamps every score to +-131008 (softmax_64.py:45-71).  A row whose extremes are
-      // inside that range needs no clamp at all; only a row that reaches it (infinities included) takes
-      // the per-element clamp.  NaN scores pass through either way and make the row NaN.
-      if (mx > kClamp || mn < -kClamp) {
+      // The reference clamps every score to +-131008 (softmax_64.py:45-71).  The clamp changes the result
+      // only when the row maximum is above the range, or so close to its lower end that a score clamped
+      // up to -131008 would still get a non-zero weight (exp2 of less than -256 * log2(e) is zero either
+      // way); such rows, infinities included, take the per-element clamp.  NaN scores pass through and
+      // make the row NaN in both cases.
+      if (mx > kClamp || mx < -kClamp + 256.0f) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) v[j] = clamp_keep_nan(v[j]);
         mx = fmaxf(fminf(mx, kClamp), -kClamp);
