@@ -344,6 +344,31 @@ def test_fused_attention_nan_and_infinite_bias_rows(ops) -> None:
     torch.testing.assert_close(got[0, 3, :32], v.float()[0, 5, :32], rtol=1e-2, atol=1e-2)
 
 
+def test_fused_attention_rows_at_the_edges_of_the_clamp_range(ops) -> None:
+    """softmax_64 clamps scores to +-131008 (softmax_64.py:45-71).  Rows far inside the range skip the
+    clamp in the fused kernel; rows whose maximum sits at either end of the range must still agree with
+    the oracle: a row pushed below the lower end flattens, a row with finite huge values saturates."""
+    batch, heads, d = 1, 4, 128
+    q, k, v = (_bf(torch.randn((batch, 64, d), generator=_gen(75 + i))) for i in range(3))
+    bias = torch.zeros((batch, heads, 64, 64))
+    bias[0, 0, 2, :] = -131072.0          # every score below the range: clamped to one value plus q.k
+    bias[0, 0, 4, :] = -131072.0
+    bias[0, 0, 4, 9] = -130048.0          # ... except one key just inside it, which takes all the weight
+    bias[0, 1, 6, :] = -130944.0 + 0.0    # maximum within 256 of the lower end (rounds to a bf16 value)
+    bias[0, 1, 6, 11] = -131072.0
+    bias[0, 2, 8, 3] = 3.0e38             # finite, far above the range: clamped, the key still wins
+    bias[0, 3, 10, :] = 65280.0           # large but inside: ordinary softmax of the scores
+    bias = _bf(bias)
+    out = torch.empty((batch, 64, d), dtype=BF16, device="cuda")
+    ops.attention(out, _dev(q), _dev(k), _dev(v), _dev(bias), 0.2, batch, heads)
+    want = O.attention_v(O.softmax_64(O.body_qk(q, k, 0.2, heads), bias), v)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all() and torch.isfinite(want).all()
+    torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got[0, 4, :32], v.float()[0, 9, :32], rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(got[0, 8, 64:96], v.float()[0, 3, 64:96], rtol=1e-2, atol=1e-2)
+
+
 # ------------------------------------------------------------------ batched matmuls
 
 def test_body_qk_matches_explicit_head_reshape(ops) -> None:
