@@ -213,6 +213,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t out_buf = out_base + (warp - 2) * (32 * 64);
     constexpr float kLog2e = 1.4426950408889634f;
     bool ok = true;
+    // O row of pair `j_pair` (the j-th pair of this CTA): 32 outputs, scaled by 1 / sum, to this warp's
+    // staging box, then a TMA store.
+    auto finish_output = [&](long long j_pair, uint32_t j, float row_sum) -> bool {
+      const uint32_t t = j & 1u;
+      if (!ptx::mbar_wait(bar_o_full + 8 * t, (j >> 1) & 1u, abort_flag, p.status, 0x680u + t)) return false;
+      ptx::tc_fence_after_sync();
+      uint32_t oraw[32];
+      ptx::tmem_ld_32x32(tmem_base + kColO + t * 32 + lane_sel, oraw);
+      ptx::tc_wait_ld();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(bar_o_empty + 8 * t);
+        ptx::bulk_wait_read<0>();  // the previous store of this warp has read the staging box
+      }
+      __syncwarp();
+      const float inv = 1.0f / row_sum;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k2 = 0; k2 < 4; ++k2) {
+          w[k2] = pack_bf16x2(__uint_as_float(oraw[c * 8 + 2 * k2]) * inv, __uint_as_float(oraw[c * 8 + 2 * k2 + 1]) * inv);
+        }
+        // 32 rows x 64 bytes in the 64-byte swizzle: 16-byte chunk c of row q lives at chunk c ^ ((q >> 1) & 3)
+        ptx::st_shared_v4(out_buf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const long long item = 2 * j_pair + e;
+        const int b = static_cast<int>(item / p.heads), h = static_cast<int>(item % p.heads);
+        ptx::tma_store_2d(&map_out, out_buf, h * 32, b * 64 + (quarter & 1) * 32);
+        ptx::bulk_commit();
+      }
+      return true;
+    };
+    bool have_pending = false;
+    long long pending_pair = 0;
+    uint32_t pending_i = 0;
+    float pending_sum = 1.0f;
     uint32_t i = 0;
     for (long long pair = blockIdx.x; pair < p.pairs && ok; pair += gridDim.x, ++i) {
       const uint32_t s = i % kStages, t = i & 1u;
@@ -289,40 +330,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_p_full + 8 * t);
 
-      // O row: 32 outputs, scaled by 1 / sum, to this warp's staging box, then a TMA store
-      ok = ptx::mbar_wait(bar_o_full + 8 * t, (i >> 1) & 1u, abort_flag, p.status, 0x680u + t);
-      if (!ok) break;
-      ptx::tc_fence_after_sync();
-      uint32_t oraw[32];
-      ptx::tmem_ld_32x32(tmem_base + kColO + t * 32 + lane_sel, oraw);
-      ptx::tc_wait_ld();
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        ptx::mbar_arrive(bar_o_empty + 8 * t);
-        ptx::bulk_wait_read<0>();  // the previous store of this warp has read the staging box
+      // The O rows of this pair are finished one round later, after the next softmax of this
+      // warpgroup: the second product and its barrier round trip then never make it wait.
+      if (have_pending) {
+        ok = finish_output(pending_pair, pending_i, pending_sum);
+        if (!ok) break;
       }
-      __syncwarp();
-      const float inv = 1.0f / sum;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          w[j] = pack_bf16x2(__uint_as_float(oraw[c * 8 + 2 * j]) * inv, __uint_as_float(oraw[c * 8 + 2 * j + 1]) * inv);
-        }
-        // 32 rows x 64 bytes in the 64-byte swizzle: 16-byte chunk c of row q lives at chunk c ^ ((q >> 1) & 3)
-        ptx::st_shared_v4(out_buf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
-      }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        const long long item = 2 * pair + e;
-        const int b = static_cast<int>(item / p.heads), h = static_cast<int>(item % p.heads);
-        ptx::tma_store_2d(&map_out, out_buf, h * 32, b * 64 + (quarter & 1) * 32);
-        ptx::bulk_commit();
-      }
+      have_pending = true;
+      pending_pair = pair;
+      pending_i = i;
+      pending_sum = sum;
     }
+    if (ok && have_pending) finish_output(pending_pair, pending_i, pending_sum);
     if (lane == 0) ptx::bulk_wait_read<0>();
     __syncwarp();
   }
