@@ -11,6 +11,12 @@
  *    never synchronises (lc0b200_device_status is the one exception: it synchronises
  *    the device to read the flag word).  In-place use (out == in) is allowed wherever
  *    the reference graph does it.
+ *  - Every call works on the CUDA device that is current in the calling thread; what the
+ *    library keeps between calls (device addresses of its own symbols, kernel attributes,
+ *    SM counts) is kept per device behind a mutex, so one process may drive several GPUs
+ *    from several threads.  A failed kernel launch is reported by the call that made it
+ *    and cleared; composite entry points (fused_qkv_projection, linear_int8*, net_forward)
+ *    may have launched part of their kernels when they return an error.
  *  - Citations "K/x.py" are packages/lczero-triton/src/lczero_triton/bt4/kernels/x.py,
  *    "N" is packages/lczero-triton/src/lczero_triton/bt4/network.py and "T/x.py" is
  *    packages/lczero-triton/tests/x.py of the reference.
@@ -58,8 +64,8 @@ enum { LC0B200_W_KN = 0, LC0B200_W_NK = 1 };
 
 LC0B200_API const char* lc0b200_version(void);
 LC0B200_API const char* lc0b200_status_string(int status);
-/* Synchronises the current device and returns LC0B200_ERR_DEVICE_TIMEOUT if any kernel gave up
- * since the last call (detail_host[0..3] receives the flag words, may be NULL); clears the flag.
+/* Synchronises the current device and returns LC0B200_ERR_DEVICE_TIMEOUT if any kernel on that device
+ * gave up since the last call (detail_host[0..3] receives the flag words, may be NULL); clears the flag.
  * Word 0 says why: 1 = a bounded wait ran out (word 1 = which wait, word 2 = CTA), 2 = a kernel
  * found its shared-memory window not 1024-byte aligned and did nothing (word 1 = the address). */
 LC0B200_API int lc0b200_device_status(unsigned int* detail_host);
@@ -180,7 +186,7 @@ LC0B200_API int lc0b200_transpose(void* dst, const void* src, int rows, int cols
  * out = (v - mean) / sqrt(var + epsilon) * gamma + beta, population variance, fp32 math.
  * alpha points at one bf16 element.  skip / alpha may be NULL when has_skip == 0.
  * If q_out_int8 and q_scale_f32 are non-NULL the normalised row (as rounded to bf16) is additionally
- * quantised per row (see lc0b200_quantize_rows) — no reference counterpart; out_bf16 may then be
+ * quantised per row (the multiply-by-reciprocal rule of lc0b200_quantize_rows) — no reference counterpart; out_bf16 may then be
  * NULL to store the quantised form only. */
 LC0B200_API int lc0b200_layer_norm(void* out_bf16, const void* in_bf16, const void* bias_bf16, const void* skip_bf16,
                        const void* gamma_bf16, const void* beta_bf16, const void* alpha_bf16,
@@ -192,12 +198,20 @@ LC0B200_API int lc0b200_softmax_64(void* out_bf16, const void* scaled_qk_bf16, c
 /* Fused edge-biased attention for the 64-token board: N:1004-1047 (K/batched_matmul.py body_qk,
  * K/softmax_64.py, K/batched_matmul.py body_attention_v) in one kernel, scores never leave the SM.
  * q/k/v rows are tokens with heads interleaved in the channel dimension; ld* are row pitches in
- * elements; bias is [B, H, 64, 64] bf16 (may be NULL); depth (per-head width) must be 32. */
+ * elements; bias is [B, H, 64, 64] bf16 (may be NULL); depth (per-head width) must be 32.
+ * Non-finite scores behave as in K/softmax_64.py (clamp, NaN kept in its row).  One deviation for
+ * non-finite V: with an even head count heads 2j and 2j+1 share one 128-row tensor-core product, and
+ * an Inf or NaN in V of one of them also turns the other's outputs for that position into NaN
+ * (0 x Inf); the reference keeps it inside the head, as the odd-head-count kernel here does. */
 LC0B200_API int lc0b200_attention(void* out_bf16, const void* q_bf16, const void* k_bf16, const void* v_bf16,
                       const void* bias_bf16, float scale, long long batch_size, int heads, int depth,
                       long long ldq, long long ldk, long long ldv, long long ldo, void* stream);
 /* Symmetric per-row int8 quantisation (no reference counterpart; the reference has no int8 path):
- * s = max|x| / 127 (1 if the row is all zero), q = clamp(rint(x / s), -127, 127), round-half-even. */
+ * scale s = max|x| / 127 (1 if the row is all zero) is what is stored, and the rounding uses ONE
+ * reciprocal per row: inv = 127 / max|x| (IEEE division, fp32), q = rint(fp32(x * inv)), round-half-even,
+ * saturated to [-127, 127].  This is not the same as rint(x / s) in last-bit ties; a caller that wants to
+ * reproduce the bytes must use the multiply form.  (Weights, quantised once at upload, use IEEE
+ * division by the per-channel scale: q = rint(w / s).) */
 LC0B200_API int lc0b200_quantize_rows(void* out_int8, float* scale_f32, const void* in_bf16, long long row_count,
                           int width, long long ld_in, void* stream);
 /* Rows of a deferred LayerNorm straight to per-row int8 (no reference counterpart): with mean / rstd of
@@ -258,10 +272,12 @@ LC0B200_API int lc0b200_policy_tail(float* out_f32, const void* records_bf16, co
 /* The step right after the path in lc0 (BT4_PLAN.md:42-43: the graph emits raw WDL logits and the
  * runtime applies the softmax on the host): wdl_probs = softmax(wdl_logits) over 3, policy_probs =
  * softmax of the policy logits over the legal moves only (legal_mask[b,o] != 0; NULL = all legal;
- * illegal entries get 0; a position without legal moves gets all zeros).  Either output may be NULL. */
-LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits,
-                                 const float* wdl_logits, const uint8_t* legal_mask, int batch_size,
-                                 int policy_size, void* stream);
+ * illegal entries get 0; a position without legal moves gets all zeros), and the search's value pair
+ * (BT4_PLAN.md:753 "Host WDL softmax and Q/D conversion"): q_d[b] = (Q, D) = (W - L, D) of those
+ * probabilities, Q in [-1, 1] from the side to move.  Any output may be NULL, but not all three. */
+LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, float* q_d,
+                                 const float* policy_logits, const float* wdl_logits, const uint8_t* legal_mask,
+                                 int batch_size, int policy_size, void* stream);
 
 /* ---- the whole forward pass as one object -------------------------------------------------
  *

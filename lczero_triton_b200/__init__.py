@@ -18,13 +18,13 @@ import importlib
 _LAZY = {
     "load_network": "format", "save_network": "format", "normalize_network": "format",
     "validate_network_format": "format", "NetworkFormatError": "format", "Network": "format",
-    "Bt4Net": "net", "NetConfig": "config", "CONFIGS": "config",
+    "Bt4Net": "net", "NativeNet": "native", "ShardedNet": "sharded", "NetConfig": "config", "CONFIGS": "config",
 }
 
 
 def __getattr__(name: str):
     if name in _LAZY:
         return getattr(importlib.import_module(f"{__name__}.{_LAZY[name]}"), name)
-    if name in ("ops", "net", "format", "config", "weights", "synthetic", "mapping_table", "sharding", "build"):
+    if name in ("ops", "net", "format", "config", "weights", "synthetic", "mapping_table", "sharded", "native", "build"):
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -70,7 +70,7 @@ SIGNATURES: dict[str, tuple] = {
     "lc0b200_embed_position_input": (_P, _P, _P, _I, _P),
     "lc0b200_embed_concat": (_P, _P, _P, _P, _I, _I, _P),
     "lc0b200_policy_tail": (_P, _P, _P, _P, _P, _I, _I, _P),
-    "lc0b200_output_probabilities": (_P, _P, _P, _P, _P, _I, _I, _P),
+    "lc0b200_output_probabilities": (_P, _P, _P, _P, _P, _P, _I, _I, _P),
     "lc0b200_net_arena_bytes": (_P, _I),
     "lc0b200_net_create": (POINTER(c_void_p), _P, _I, _P, ctypes.c_size_t),
     "lc0b200_net_destroy": (_P,),

@@ -2,6 +2,9 @@
 // Nothing here allocates, synchronises (except lc0b200_device_status) or throws.
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "common.cuh"
 #include "gemm.h"
 #include "kernels.h"
@@ -10,14 +13,30 @@ namespace lc0b200 {
 
 static __device__ unsigned int g_device_status[4] = {0u, 0u, 0u, 0u};
 
-unsigned int* device_status_words() {
-  static unsigned int* cached = nullptr;
-  if (cached == nullptr) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
-    cached = reinterpret_cast<unsigned int*>(p);
+namespace {
+std::mutex g_device_mutex;
+DeviceInfo g_device_info[kMaxDevices];
+std::atomic<bool> g_device_known[kMaxDevices];
+}  // namespace
+
+// In host code `g_device_status` is a handle, not an address: the address a kernel can use differs
+// from device to device and is asked for once per device, with that device current.
+const DeviceInfo* device_info() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  if (g_device_known[device].load(std::memory_order_acquire)) return &g_device_info[device];
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  if (!g_device_known[device].load(std::memory_order_relaxed)) {
+    void* status = nullptr;
+    int sms = 0;
+    if (cudaGetSymbolAddress(&status, g_device_status) != cudaSuccess || status == nullptr) return nullptr;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) return nullptr;
+    g_device_info[device].index = device;
+    g_device_info[device].sm_count = sms;
+    g_device_info[device].status = static_cast<unsigned int*>(status);
+    g_device_known[device].store(true, std::memory_order_release);
   }
-  return cached;
+  return &g_device_info[device];
 }
 
 }  // namespace lc0b200
@@ -359,16 +378,16 @@ LC0B200_API int lc0b200_policy_tail(float* out, const void* records, const void*
   return policy_tail(out, records, keys, w, table, batch_size, width, S(stream));
 }
 
-LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits,
-                                             const float* wdl_logits, const uint8_t* legal_mask, int batch_size,
-                                             int policy_size, void* stream) {
-  if (policy_probs == nullptr && wdl_probs == nullptr) return LC0B200_ERR_NULL_POINTER;
+LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_probs, float* q_d,
+                                             const float* policy_logits, const float* wdl_logits,
+                                             const uint8_t* legal_mask, int batch_size, int policy_size, void* stream) {
+  if (policy_probs == nullptr && wdl_probs == nullptr && q_d == nullptr) return LC0B200_ERR_NULL_POINTER;
   if (policy_probs != nullptr) REQUIRE_PTR(policy_logits);
-  if (wdl_probs != nullptr) REQUIRE_PTR(wdl_logits);
+  if (wdl_probs != nullptr || q_d != nullptr) REQUIRE_PTR(wdl_logits);
   REQUIRE_SHAPE(batch_size >= 0 && policy_size > 0);
   if (batch_size == 0) return LC0B200_OK;
-  return output_probabilities(policy_probs, wdl_probs, policy_logits, wdl_logits, legal_mask, batch_size, policy_size,
-                              S(stream));
+  return output_probabilities(policy_probs, wdl_probs, q_d, policy_logits, wdl_logits, legal_mask, batch_size,
+                              policy_size, S(stream));
 }
 
 }  // extern "C"

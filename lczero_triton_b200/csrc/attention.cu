@@ -15,8 +15,6 @@
 // what the policy head uses.
 #include <cuda_runtime.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -417,25 +415,19 @@ int attention(void* out, const void* q, const void* k, const void* v, const void
   p.heads = heads;
   p.scale = scale;
   // Heads per CTA: long runs amortise the pipeline prologue; short runs keep all SMs busy when the
-  // batch is small.  LC0B200_ATTN_HPB overrides the choice (measurement aid).
-  static const int forced = []() {
-    const char* v = getenv("LC0B200_ATTN_HPB");
-    return v != nullptr ? atoi(v) : 0;
-  }();
-  int hpb = forced != 0 ? forced : (p.items >= 64LL * 8 * sm_count() ? 16 : (p.items >= 16LL * 8 * sm_count() ? 8 : 4));
-  auto run = [&](auto kernel, int heads_per_block) -> int {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kStageBytes) != cudaSuccess) {
-      return LC0B200_ERR_CUDA;
-    }
+  // batch is small.
+  const int hpb = p.items >= 64LL * 8 * sm_count() ? 16 : (p.items >= 16LL * 8 * sm_count() ? 8 : 4);
+  auto run = [&](auto kernel, PerDeviceOnce& once, int heads_per_block) -> int {
+    if (allow_dynamic_smem(once, kernel, 2 * kStageBytes) != LC0B200_OK) return LC0B200_ERR_CUDA;
     const long long blocks = ceil_div_ll(p.items, heads_per_block);
     if (blocks > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
     kernel<<<static_cast<unsigned>(blocks), 128, 2 * kStageBytes, st>>>(p);
     return launch_status();
   };
-  if (hpb >= 32) return run(attention_kernel<32>, 32);
-  if (hpb >= 16) return run(attention_kernel<16>, 16);
-  if (hpb >= 8) return run(attention_kernel<8>, 8);
-  return run(attention_kernel<4>, 4);
+  static PerDeviceOnce once16, once8, once4;
+  if (hpb >= 16) return run(attention_kernel<16>, once16, 16);
+  if (hpb >= 8) return run(attention_kernel<8>, once8, 8);
+  return run(attention_kernel<4>, once4, 4);
 }
 
 int batched_matmul(void* out, const void* a, const void* b, const void* scale, int operation, long long batch_count,

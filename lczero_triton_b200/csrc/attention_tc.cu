@@ -21,8 +21,6 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -358,11 +356,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 bool attention_tc_supported(const void* out, const void* q, const void* k, const void* v, const void* bias,
                             long long batch, int heads, long long ldq, long long ldk, long long ldv, long long ldo) {
-  static const bool disabled = []() {
-    const char* e = getenv("LC0B200_ATTN_IMPL");  // "mma" keeps the mma.sync kernel (measurement aid)
-    return e != nullptr && e[0] == 'm';
-  }();
-  if (disabled) return false;
   if ((heads & 1) != 0 || batch <= 0) return false;
   if (!aligned16(out) || !aligned16(q) || !aligned16(k) || !aligned16(v) || (bias != nullptr && !aligned16(bias))) {
     return false;
@@ -387,14 +380,8 @@ int attention_tc(void* out, const void* q, const void* k, const void* v, const v
       !make_tensormap_2d(&mb, bias, 2, batch * heads * 64, 64, 64, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LC0B200_ERR_CUDA;
   }
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-        cudaSuccess) {
-      return LC0B200_ERR_CUDA;
-    }
-    configured = true;
-  }
+  static PerDeviceOnce smem_opt_in;
+  if (allow_dynamic_smem(smem_opt_in, attention_tc_kernel, kSmemBytes) != LC0B200_OK) return LC0B200_ERR_CUDA;
   TcParams p;
   p.pairs = batch * heads / 2;
   p.heads = heads;

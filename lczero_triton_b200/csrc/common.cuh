@@ -5,16 +5,31 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/lc0b200.h"
 
 namespace lc0b200 {
 
 using bf16 = __nv_bfloat16;
 
-// Device address of four status words.  Word 0: first device-side failure code (0 = none);
-// word 1: detail (role / barrier index); word 2: CTA; word 3: parity waited for.  Written by
-// kernels whose bounded waits ran out; read and cleared by lc0b200_device_status().
-unsigned int* device_status_words();
+// What the host side keeps per device.  Everything here is looked up once per device, with that
+// device current, under a mutex (api.cu), so one process may drive several GPUs from several threads.
+//   status: device address of four status words on THAT device.  Word 0: first device-side failure
+//   code (0 = none); word 1: detail (role / barrier index); word 2: CTA; word 3: parity waited for.
+//   Written by kernels whose bounded waits ran out; read and cleared by lc0b200_device_status().
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  int index;
+  int sm_count;
+  unsigned int* status;
+};
+// nullptr when the runtime cannot name the current device or its index is out of range.
+const DeviceInfo* device_info();
+inline unsigned int* device_status_words() {
+  const DeviceInfo* d = device_info();
+  return d != nullptr ? d->status : nullptr;
+}
 
 constexpr unsigned int kDeviceWaitTimeout = 1;
 constexpr unsigned int kDeviceSmemMisaligned = 2;  // a kernel found its shared-memory window not 1024-byte aligned
@@ -78,17 +93,34 @@ __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpr
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// SM count of the current device.
 inline int sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-    cached = n;
-  }
-  return cached;
+  const DeviceInfo* d = device_info();
+  return d != nullptr ? d->sm_count : 148;
 }
 
-inline int launch_status() { return cudaPeekAtLastError() == cudaSuccess ? LC0B200_OK : LC0B200_ERR_CUDA; }
+// A kernel's opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: one flag per
+// device for each kernel (a static PerDeviceOnce beside the launch).  Racing first calls both set the
+// attribute, which is harmless.
+struct PerDeviceOnce {
+  std::atomic<bool> done[kMaxDevices];
+};
+template <typename Kernel>
+inline int allow_dynamic_smem(PerDeviceOnce& once, Kernel kernel, int bytes) {
+  const DeviceInfo* d = device_info();
+  if (d == nullptr) return LC0B200_ERR_CUDA;
+  if (once.done[d->index].load(std::memory_order_acquire)) return LC0B200_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return LC0B200_ERR_CUDA;
+  }
+  once.done[d->index].store(true, std::memory_order_release);
+  return LC0B200_OK;
+}
+
+// Status of the `<<<>>>` launch just made by this thread.  cudaGetLastError also CLEARS the thread's
+// error slot, so one failed launch is reported once, by the call that made it, and neither by later
+// calls of this library nor by the host framework's own launch checks.
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? LC0B200_OK : LC0B200_ERR_CUDA; }
 
 }  // namespace lc0b200

@@ -27,8 +27,6 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "gemm.h"
 #include "ptx.cuh"
@@ -48,19 +46,11 @@ constexpr int kGroupBytes = 32 * kRowBytes;  // staging for 32 rows x 64 bf16 co
 //   kRes  : y = alpha * (dequant(acc) + bias) + skip, skip plain or a deferred LayerNorm; row sums out
 enum : int { kPlain = 0, kLnIn = 1, kRes = 2 };
 
-// How the grouped epilogue (bf16 results, 64-column groups) gets a tile to global memory:
-//   kStoreTma   : staged in shared memory, TMA store (any row length a tensor map takes; asynchronous,
-//                 but its shared-memory reads compete with the tensor core's operand reads: about
-//                 1100 clocks per 128 x 256 tile)
-//   kStoreDirect: straight from registers, 32 bytes (one sector) per lane and store; touches no shared
-//                 memory, but the epilogue warps wait on the store path (a row per lane drains slowly)
-// Measured per shape (a third way, warps copying the staged tile out in 128-byte lines, never won): in
-// short bursts direct stores win where the main loop is long (K >= 1536), but launched back to back
-// under the power cap the TMA store costs the least energy per launch for every shape, so it is the
-// default; LC0B200_GEMM_STORE selects the others for measurements.
-//   kStoreMixed : even groups staged and stored by TMA, odd groups straight from registers (half of each cost)
-enum : int { kStoreTma = 0, kStoreMixed = 1, kStoreDirect = 2 };
-
+// The grouped epilogue (bf16 results, 64-column groups) stages a tile in shared memory and stores it by
+// TMA (any row length a tensor map takes; asynchronous).  Stores straight from registers (32 bytes per
+// lane) and a half-and-half mix were measured too: they win short bursts where the main loop is long,
+// but launched back to back under the power cap the TMA store costs the least energy per launch for
+// every shape of the forward pass, so it is the only form kept.
 template <int BN, int CTAS, int MODE>
 struct TileCfg {
   static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are used for 256 x 256 tiles only");
@@ -86,10 +76,7 @@ struct TileCfg {
   static constexpr int kFixedBytes = kStagingBytes + 512 /*barriers*/ + kVecBytes;
   // As many pipeline stages as fit below the 227 KB per-CTA limit (at most 8).
   static constexpr int kFit = (227 * 1024 - kFixedBytes) / kStageBytes;
-#ifndef LC0B200_GEMM_MAX_STAGES
-#define LC0B200_GEMM_MAX_STAGES 8
-#endif
-  static constexpr int kStages = kFit > LC0B200_GEMM_MAX_STAGES ? LC0B200_GEMM_MAX_STAGES : kFit;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
   static_assert(kStages >= 3, "pipeline too shallow");
   static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
 };
@@ -107,7 +94,6 @@ struct KernelParams {
   int activation;
   int vec_ok;     // out / bias / scales / fold vectors are 16-byte aligned and ldc keeps rows aligned
   int tma_store;  // bf16 output that a tensor map can address (map_out is valid)
-  int store_mode;  // how the grouped epilogue writes its results: kStoreTma or kStoreDirect
   unsigned int* status;
   // Deferred LayerNorm (see lc0b200_gemm_args).
   const float2* ln_in_stats;
@@ -434,22 +420,6 @@ __device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* 
   return __uint_as_float(raw);
 }
 
-// Wait-time accounting for tuning (compiled in with -DLC0B200_GEMM_PROFILE only): cycles each role
-// spends blocked, summed over CTAs.  [0] producer on a free stage, [1] MMA issuer on a free
-// accumulator, [2] MMA issuer on operands, [3] epilogue warp 0 on a complete accumulator,
-// [4] epilogue warp 0 from accumulator complete to accumulator released, [5] the same warp's
-// remaining tile time (fence + stores), [6] whole-kernel cycles of thread 0, [7] CTAs.
-#ifdef LC0B200_GEMM_PROFILE
-__device__ unsigned long long g_gemm_profile[16];
-__device__ __forceinline__ long long prof_now() { return clock64(); }
-__device__ __forceinline__ void prof_add(int slot, long long cycles) {
-  atomicAdd(&g_gemm_profile[slot], static_cast<unsigned long long>(cycles));
-}
-#else
-__device__ __forceinline__ long long prof_now() { return 0; }
-__device__ __forceinline__ void prof_add(int, long long) {}
-#endif
-
 template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
 __global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -500,7 +470,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int n_tiles = (p.n + BN - 1) / BN;
   const long long num_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.k + kElemsPerRow - 1) / kElemsPerRow;
-  const long long prof_start = prof_now();
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -543,15 +512,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    long long prof_wait = 0;
     for (long long tile = group; tile < num_tiles && ok; tile += num_groups) {
       const int m0 = static_cast<int>(tile / n_tiles) * kTileM + static_cast<int>(rank) * kBM;
       const int n0 = static_cast<int>(tile % n_tiles) * BN + static_cast<int>(rank) * Cfg::kBRows;
       for (int kb = 0; kb < k_blocks; ++kb) {
-        const long long prof_t = prof_now();
         ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
         ok = __all_sync(0xFFFFFFFFu, ok);
-        prof_wait += prof_now() - prof_t;
         if (!ok) break;
         if (ptx::elect_one()) {
           // Transaction bytes of both CTAs complete on the leader's barrier.
@@ -575,7 +541,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
     }
-    if (lane == 0) prof_add(0, prof_wait);
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -586,28 +551,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      long long prof_acc = 0, prof_ops = 0, prof_first = 0, prof_early = 0, prof_late_blocks = 0, prof_blocks = 0;
       for (long long tile = group; tile < num_tiles && ok; tile += num_groups, ++local) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        const long long prof_t = prof_now();
         ok = ptx::mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 0x200u + acc);
         ok = __all_sync(0xFFFFFFFFu, ok);
-        prof_acc += prof_now() - prof_t;
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          const long long prof_t2 = prof_now();
           ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 0x300u + stage);
           ok = __all_sync(0xFFFFFFFFu, ok);
-          {
-            const long long waited = prof_now() - prof_t2;
-            prof_ops += waited;
-            if (kb == 0) prof_first += waited; else if (kb < 4) prof_early += waited;
-            prof_late_blocks += waited > 100 ? 1 : 0;
-            prof_blocks += 1;
-          }
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_a + stage * Cfg::kABytes;
@@ -635,14 +589,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit<CTAS>(bar_acc_full + 8 * acc);  // accumulator complete -> epilogue (both CTAs)
       }
-      if (lane == 0) {
-        prof_add(1, prof_acc);
-        prof_add(2, prof_ops);
-        prof_add(8, prof_first);
-        prof_add(9, prof_early);
-        prof_add(10, prof_late_blocks);
-        prof_add(11, prof_blocks);
-      }
     }
     __syncwarp();
   } else {
@@ -655,12 +601,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t staging_warp = staging_base + ew * Cfg::kBuffersPerWarp * kGroupBytes;
     const uint32_t skip_bar = bar_skip + 8 * ew;
     const bool tma_path = Cfg::kTmaStore && p.tma_store && p.out_kind == LC0B200_OUT_BF16;  // grouped epilogue
-    const int store_mode = p.store_mode;
-    const bool any_staged = store_mode != kStoreDirect;  // some results pass through the staging buffers
     uint32_t local = 0;
     uint32_t skip_phase = 0;  // parity of this warp's skip barrier; flips each time the barrier is used
     bool ok = true;
-    long long prof_wait = 0, prof_math = 0, prof_store = 0, prof_ld = 0, prof_alu = 0;
     // Column of the tile this thread carries to the vector area (threads past BN carry none).
     const int vec_col = static_cast<int>(threadIdx.x) - 64;
     ColRegs cols = {};
@@ -708,7 +651,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       rc.nmean = (MODE == kRes) ? -rc.mean * rc.rstd : -rc.mean;
-      if (tma_path && any_staged) {
+      if (tma_path) {
         // TMA-store flavours: the staging buffers are free once the previous tile's stores have
         // finished reading them.
         if (lane == 0) ptx::bulk_wait_read<0>();
@@ -717,11 +660,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if constexpr (MODE == kRes) {
         // Bring this warp's part of the skip operand (32 rows x kColsPerWarp columns) into its staging
         // buffers, one 32 x 64 box per group.
-        if (store_mode != kStoreTma) {
-          // Some buffers were last read by ordinary shared-memory loads of this warp only.
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-        }
         if (lane == 0) {
           int boxes = 0;
 #pragma unroll
@@ -740,10 +678,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
       }
 
-      const long long prof_t = prof_now();
       ok = ptx::mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status, 0x400u + acc);
-      const long long prof_t1 = prof_now();
-      prof_wait += prof_t1 - prof_t;
       if (!ok) break;
       ptx::tc_fence_after_sync();
       if constexpr (MODE == kRes) {
@@ -776,7 +711,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int g = 0; g < groups_here; ++g) {
             const int col0 = n0 + g * 64;  // a partly outside group is clipped by the store
             uint32_t v[64];
-            const long long prof_g0 = prof_now();
             ptx::tmem_ld_32x32(taddr_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             ptx::tmem_ld_32x32(taddr_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             ptx::tc_wait_ld();
@@ -793,10 +727,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
               }
             }
-            const long long prof_g1 = prof_now();
-            prof_ld += prof_g1 - prof_g0;
-            bf16* const out_row = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;  // direct stores
-            const bool staged = store_mode == kStoreTma || (store_mode == kStoreMixed && (g & 1) == 0);
             float sum = 0.0f, sumsq = 0.0f;
             // Row `lane` of this group's 32 x 128-byte staging buffer (skip operand in, results out)
             // in the 128-byte swizzle the tensor maps use: 16-byte chunk c of row r lives at
@@ -818,19 +748,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               uint32_t pk[16];
               finish32_sv<MODE, INT8, BN>(&v[h * 32], pk, skip_raw, rc, p, sum, sumsq, vec_base,
                                           half * kColsPerWarp + g * 64 + h * 32);
-              if (staged) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                  ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
-                                    pk[4 * c + 2], pk[4 * c + 3]);
-                }
-              } else if (row_ok) {
-                // n is a multiple of 16 here: each 16-column piece is wholly inside or outside.
-                if (col0 + h * 32 < p.n) ptx::st_global_v8(out_row + h * 32, &pk[0]);
-                if (col0 + h * 32 + 16 < p.n) ptx::st_global_v8(out_row + h * 32 + 16, &pk[8]);
+              for (int c = 0; c < 4; ++c) {
+                ptx::st_shared_v4(row_addr + (((h * 4 + c) ^ (lane & 7)) << 4), pk[4 * c], pk[4 * c + 1],
+                                  pk[4 * c + 2], pk[4 * c + 3]);
               }
             }
-            prof_alu += prof_now() - prof_g1;
             if (MODE == kRes) {
               // One partial per 64 output columns: part index col0 / 64, layout [part][row].
               if (p.stats_out != nullptr && row_ok) p.stats_out[(col0 >> 6) * p.m + row] = make_float2(sum, sumsq);
@@ -840,8 +763,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_vec_free);
           released = true;
-          prof_math += prof_now() - prof_t1;
-          if (any_staged && n0 < p.n) {
+          if (n0 < p.n) {
             // One proxy fence per tile and warp (by far the most expensive instruction here), then
             // the stores of all groups; a group partly outside the matrix is clipped by the store.
             ptx::fence_proxy_async_smem();
@@ -849,7 +771,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) {
 #pragma unroll
               for (int g = 0; g < Cfg::kGroups; ++g) {
-                if (n0 + g * 64 < p.n && (store_mode == kStoreTma || (g & 1) == 0)) {
+                if (n0 + g * 64 < p.n) {
                   ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
                                     static_cast<int>(m0) + quarter * 32);
                 }
@@ -926,16 +848,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       }
-      prof_store += prof_now() - prof_t1;
     }
-    if (ew == 0 && lane == 0) {
-      prof_add(3, prof_wait);
-      prof_add(4, prof_math);
-      prof_add(5, prof_store - prof_math);
-      prof_add(12, prof_ld);
-      prof_add(13, prof_alu);
-    }
-    if (tma_path && any_staged && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
+    if (tma_path && lane == 0) ptx::bulk_wait_read<0>();  // staging must outlive the last store's read
     __syncwarp();
   }
 
@@ -945,8 +859,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // Neither CTA of a pair may leave while the other can still signal its barriers or read its smem.
   if (CTAS == 2) ptx::cluster_sync();
   if (threadIdx.x == 0) {
-    prof_add(6, prof_now() - prof_start);
-    prof_add(7, 1);
   }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
@@ -959,44 +871,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------- host side
-
-#ifdef LC0B200_GEMM_PROFILE
-}  // namespace
-}  // namespace lc0b200
-// Copies the eight wait-time counters to `out8` (host memory) and zeroes them.  Synchronises the device.
-extern "C" __attribute__((visibility("default"))) int lc0b200_debug_gemm_profile(unsigned long long* out8) {  // 16 counters
-  unsigned long long zero[16] = {0};
-  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-  if (cudaMemcpyFromSymbol(out8, lc0b200::g_gemm_profile, sizeof(zero)) != cudaSuccess) return 1;
-  if (cudaMemcpyToSymbol(lc0b200::g_gemm_profile, zero, sizeof(zero)) != cudaSuccess) return 1;
-  return 0;
-}
-namespace lc0b200 {
-namespace {
-#endif
-
-// LC0B200_GEMM_PAIRS=0 in the environment keeps every GEMM on the single-CTA kernel (measurement aid).
-bool pair_kernels_enabled() {
-  static const bool enabled = []() {
-    const char* v = getenv("LC0B200_GEMM_PAIRS");
-    return !(v != nullptr && v[0] == '0');
-  }();
-  return enabled;
-}
-
-// LC0B200_GEMM_STORE=tma|mixed|direct in the environment forces one store mode wherever the output
-// allows it (measurement aid); unset, the mode follows the shape.
-int forced_store_mode() {
-  static const int mode = []() {
-    const char* v = getenv("LC0B200_GEMM_STORE");
-    if (v == nullptr) return -1;
-    if (v[0] == 't') return static_cast<int>(kStoreTma);
-    if (v[0] == 'm') return static_cast<int>(kStoreMixed);
-    if (v[0] == 'd') return static_cast<int>(kStoreDirect);
-    return -1;
-  }();
-  return mode;
-}
 
 // 2-D row-major tensor [rows, cols] with a row pitch, tiled into [box_rows, box_cols] boxes
 // whose inner extent is exactly 128 bytes (the swizzle span).
@@ -1030,13 +904,8 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
     if (!make_map(&map_skip, g.res_skip_bf16, 2, g.m, g.n, g.ld_skip, 32, 64)) return LC0B200_ERR_CUDA;
   }
   auto kernel = gemm_tcgen05_kernel<BN, INT8, W_KN, CTAS, MODE>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
-      return LC0B200_ERR_CUDA;
-    }
-    configured = true;
-  }
+  static PerDeviceOnce smem_opt_in;  // per instantiation
+  if (allow_dynamic_smem(smem_opt_in, kernel, Cfg::kSmemBytes) != LC0B200_OK) return LC0B200_ERR_CUDA;
   KernelParams p;
   p.out = g.out;
   p.bias = reinterpret_cast<const bf16*>(g.bias_bf16);
@@ -1055,12 +924,6 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
              (g.ln_in_stats == nullptr || (aligned16(g.ln_in_c) && aligned16(g.ln_in_d))) &&
              (g.res_stats == nullptr || (aligned16(g.res_gamma_bf16) && aligned16(g.res_beta_bf16)));
   p.tma_store = tma_store ? 1 : 0;
-  // Store mode of the grouped epilogue: see kStoreTma / kStoreDirect.
-  const bool direct_ok = tma_store && (reinterpret_cast<uintptr_t>(g.out) & 31u) == 0 && (g.ldc % 16) == 0 && (g.n % 16) == 0;
-  int mode = kStoreTma;  // the cheapest in energy per launch under the power cap for every shape measured
-  const int forced = forced_store_mode();
-  if (forced == kStoreTma || ((forced == kStoreDirect || forced == kStoreMixed) && direct_ok)) mode = forced;
-  p.store_mode = mode;
   p.ln_in_stats = reinterpret_cast<const float2*>(g.ln_in_stats);
   p.ln_in_c = g.ln_in_c;
   p.ln_in_d = g.ln_in_d;
@@ -1091,8 +954,11 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = CTAS == 2 ? 1 : 0;
-  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, p) != cudaSuccess) return LC0B200_ERR_CUDA;
-  return launch_status();
+  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, p) != cudaSuccess) {
+    (void)cudaGetLastError();  // reported here; do not leave it for an unrelated later call
+    return LC0B200_ERR_CUDA;
+  }
+  return LC0B200_OK;
 }
 
 // Rows at and above which the 256-wide tiles are shared by CTA pairs (below it there are too few
@@ -1113,7 +979,7 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   while (bn > kMinBn && (bn / 2 >= g.n || tiles(bn) < enough)) bn /= 2;
   if (bn == 256) {
     // (Short main loops are paced by the output and measured faster on single CTAs.)
-    if (g.m >= kPairMinRows && g.k > 512 && pair_kernels_enabled()) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
+    if (g.m >= kPairMinRows && g.k > 512) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
   if constexpr (kMinBn <= 128) {

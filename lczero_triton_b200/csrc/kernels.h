@@ -57,7 +57,8 @@ int attention_tc(void* out, const void* q, const void* k, const void* v, const v
 
 // policy.cu
 int promotion_logits(void* records, const void* keys, const void* w, int batch, int width, cudaStream_t st);
-int output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits, const float* wdl_logits,
+int output_probabilities(float* policy_probs, float* wdl_probs, float* q_d, const float* policy_logits,
+                         const float* wdl_logits,
                          const uint8_t* legal, int batch, int policy_size, cudaStream_t st);
 int policy_tail(float* out, const void* records, const void* keys, const void* w, const int32_t* table, int batch,
                 int width, cudaStream_t st);

@@ -77,9 +77,11 @@ __global__ void __launch_bounds__(256) policy_tail_kernel(float* __restrict__ ou
   }
 }
 
-// Output probabilities: WDL softmax and policy softmax over the legal moves, one CTA per position.
+// Output probabilities: WDL softmax, (Q, D) = (W - L, D), and policy softmax over the legal moves, one CTA
+// per position.
 __global__ void __launch_bounds__(256) output_probabilities_kernel(float* __restrict__ policy_probs,
                                                                    float* __restrict__ wdl_probs,
+                                                                   float* __restrict__ q_d,
                                                                    const float* __restrict__ policy_logits,
                                                                    const float* __restrict__ wdl_logits,
                                                                    const uint8_t* __restrict__ legal, int policy_size) {
@@ -87,14 +89,20 @@ __global__ void __launch_bounds__(256) output_probabilities_kernel(float* __rest
   __shared__ float bcast;
   const long long b = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (wdl_probs != nullptr && threadIdx.x == 0) {
+  if ((wdl_probs != nullptr || q_d != nullptr) && threadIdx.x == 0) {
     const float w = wdl_logits[b * 3], d = wdl_logits[b * 3 + 1], l = wdl_logits[b * 3 + 2];
     const float m = fmaxf(w, fmaxf(d, l));
     const float ew = expf(w - m), ed = expf(d - m), el = expf(l - m);
     const float inv = 1.0f / (ew + ed + el);
-    wdl_probs[b * 3] = ew * inv;
-    wdl_probs[b * 3 + 1] = ed * inv;
-    wdl_probs[b * 3 + 2] = el * inv;
+    if (wdl_probs != nullptr) {
+      wdl_probs[b * 3] = ew * inv;
+      wdl_probs[b * 3 + 1] = ed * inv;
+      wdl_probs[b * 3 + 2] = el * inv;
+    }
+    if (q_d != nullptr) {
+      q_d[b * 2] = ew * inv - el * inv;
+      q_d[b * 2 + 1] = ed * inv;
+    }
   }
   if (policy_probs == nullptr) return;
   const float* logits = policy_logits + b * policy_size;
@@ -138,9 +146,9 @@ __global__ void __launch_bounds__(256) output_probabilities_kernel(float* __rest
 
 }  // namespace
 
-int output_probabilities(float* policy_probs, float* wdl_probs, const float* policy_logits, const float* wdl_logits,
-                         const uint8_t* legal, int batch, int policy_size, cudaStream_t st) {
-  output_probabilities_kernel<<<batch, 256, 0, st>>>(policy_probs, wdl_probs, policy_logits, wdl_logits, legal,
+int output_probabilities(float* policy_probs, float* wdl_probs, float* q_d, const float* policy_logits,
+                         const float* wdl_logits, const uint8_t* legal, int batch, int policy_size, cudaStream_t st) {
+  output_probabilities_kernel<<<batch, 256, 0, st>>>(policy_probs, wdl_probs, q_d, policy_logits, wdl_logits, legal,
                                                      policy_size);
   return launch_status();
 }

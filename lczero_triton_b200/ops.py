@@ -264,13 +264,15 @@ def policy_tail(out: torch.Tensor, records: torch.Tensor, keys: torch.Tensor, w:
 
 
 def output_probabilities(policy_logits: torch.Tensor, wdl_logits: torch.Tensor,
-                         legal_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
-    """WDL softmax and policy softmax over the legal moves (``legal_mask`` uint8 [B,1858], None = all)."""
+                         legal_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """WDL softmax, policy softmax over the legal moves (``legal_mask`` uint8 [B,1858], None = all) and the
+    search's value pair ``q_d[b] = (W - L, D)``.  Returns ``(policy_probs, wdl_probs, q_d)``."""
     _require(policy_logits, torch.float32, "policy_logits"); _require(wdl_logits, torch.float32, "wdl_logits")
     if legal_mask is not None:
         _require(legal_mask, torch.uint8, "legal_mask")
     batch, size = policy_logits.shape
     policy, wdl = torch.empty_like(policy_logits), torch.empty_like(wdl_logits)
-    check(_lib.load().lc0b200_output_probabilities(_p(policy), _p(wdl), _p(policy_logits), _p(wdl_logits),
+    q_d = torch.empty((batch, 2), dtype=torch.float32, device=wdl_logits.device)
+    check(_lib.load().lc0b200_output_probabilities(_p(policy), _p(wdl), _p(q_d), _p(policy_logits), _p(wdl_logits),
                                                    _p(legal_mask), batch, size, _stream()), "output_probabilities")
-    return policy, wdl
+    return policy, wdl, q_d

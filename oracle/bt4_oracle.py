@@ -189,15 +189,16 @@ def policy_map(records: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 
 def output_probabilities(policy_logits: torch.Tensor, wdl_logits: torch.Tensor,
-                         legal_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+                         legal_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """What lc0 does right after the graph (BT4_PLAN.md:42-43: the graph emits raw WDL logits, the
-    softmax is applied on the host): WDL softmax, and the policy softmax over the legal moves only."""
+    softmax is applied on the host; BT4_PLAN.md:753 "Host WDL softmax and Q/D conversion"): WDL softmax,
+    the policy softmax over the legal moves only, and ``(Q, D) = (W - L, D)``."""
     wdl = torch.softmax(wdl_logits.float(), dim=-1)
     logits = policy_logits.float()
     if legal_mask is not None:
         logits = torch.where(legal_mask != 0, logits, torch.full_like(logits, float("-inf")))
     policy = torch.softmax(logits, dim=-1)
-    return torch.nan_to_num(policy, nan=0.0), wdl
+    return torch.nan_to_num(policy, nan=0.0), wdl, torch.stack((wdl[:, 0] - wdl[:, 2], wdl[:, 1]), dim=1)
 
 
 # --------------------------------------------------------------------------- whole network

@@ -11,6 +11,12 @@ generated protobuf bindings do not exist offline, so the three ``*_pb2``
 modules are replaced by attribute stubs; none of the imported functions uses
 them.  The reference functions round their result to fp16; the stored
 expectation is that fp16 tensor widened to fp32.
+
+It also writes ``tests/golden/reference_buffer_names.json``: every named buffer the reference's graph
+builder declares (``bt4/network.py``), taken from the source by an ``ast`` walk of the calls that carry
+a ``name=`` / ``output_name=`` argument - the name template as written (``{prefix}`` and ``{label}``
+left in place), the declaring helper, the expression given as the matrix's input width, and the line.
+``tests/test_buffer_names.py`` holds this package's weight table and the C network object to it.
 """
 
 from __future__ import annotations
@@ -50,8 +56,54 @@ def _stub_generated_protobuf_modules() -> None:
         sys.modules["lc0ex.proto." + name] = module
 
 
+def buffer_names(root: pathlib.Path) -> list[dict]:
+    """Named buffers of the reference graph builder, read from its source text."""
+    import ast
+
+    source = root / "packages/lczero-triton/src/lczero_triton/bt4/network.py"
+    tree = ast.parse(source.read_text())
+    rows: list[dict] = []
+
+    def template(node: ast.expr) -> str | None:
+        if isinstance(node, ast.Constant) and isinstance(node.value, str):
+            return node.value
+        if isinstance(node, ast.JoinedStr):
+            return "".join(v.value if isinstance(v, ast.Constant) else "{" + ast.unparse(v.value) + "}"
+                           for v in node.values)
+        return None  # a variable: the helper that forwards a caller's name
+
+    class Walk(ast.NodeVisitor):
+        function = None
+
+        def visit_FunctionDef(self, node: ast.FunctionDef) -> None:
+            outer, self.function = self.function, node.name
+            self.generic_visit(node)
+            self.function = outer
+
+        def visit_Call(self, node: ast.Call) -> None:
+            keywords = {k.arg: k.value for k in node.keywords if k.arg}
+            named = keywords.get("name", keywords.get("output_name"))
+            text = template(named) if named is not None else None
+            if text is not None:
+                helper = ast.unparse(node.func)
+                kind = {"_matrix_f16": "matrix", "_vector_f16": "vector",
+                        "context.builder.persistent_buffer": "constant"}.get(helper, "io")
+                rows.append({"name": text, "kind": kind, "function": self.function, "line": node.lineno,
+                             "input_width": ast.unparse(keywords["input_width"]) if "input_width" in keywords else None})
+            self.generic_visit(node)
+
+    Walk().visit(tree)
+    return rows
+
+
 def main(reference_root: str) -> None:
     root = pathlib.Path(reference_root)
+    import json
+
+    names = buffer_names(root)
+    names_target = pathlib.Path(__file__).with_name("reference_buffer_names.json")
+    names_target.write_text(json.dumps(names, indent=1) + "\n")
+    print(f"wrote {names_target} ({len(names)} named buffers)")
     _stub_generated_protobuf_modules()
     sys.path[:0] = [
         str(root / "packages/lc0ex/src"),

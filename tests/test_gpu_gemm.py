@@ -109,43 +109,6 @@ def test_bf16_gemm_store_paths_at_matrix_edges(ops, m, n, k) -> None:
     assert (wide[:m, :16] == 7.0).all() and (wide[:m, 16 + n:] == 7.0).all() and (wide[m:] == 7.0).all()
 
 
-_STORE_MODE_CHECK = """
-import sys, torch
-sys.path.insert(0, {root!r})
-from lczero_triton_b200 import _lib, ops
-from oracle import bt4_oracle as O
-torch.manual_seed(5)
-for m, n, k in ((300, 400, 1600), (8300, 1040, 1024)):
-    a = (torch.randn((m, k)) * 0.1).to(torch.bfloat16)
-    w = (torch.randn((k, n)) * 0.1).to(torch.bfloat16)
-    bias = (torch.randn(n) * 0.5).to(torch.bfloat16)
-    want = O.activate(O.matmul(a, w) + bias.float(), "mish")
-    wide = torch.full((m + 2, n + 32), 7.0, dtype=torch.bfloat16, device="cuda")
-    ops.gemm(wide[:m, 16:16 + n], a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, bias=bias.cuda(),
-             activation="mish", ldc=n + 32, w_layout=_lib.W_NK)
-    torch.testing.assert_close(wide[:m, 16:16 + n].float().cpu(), want, rtol=1e-2, atol=1e-2)
-    assert (wide[:m, :16] == 7.0).all() and (wide[:m, 16 + n:] == 7.0).all() and (wide[m:] == 7.0).all()
-assert _lib.device_status()[0] == 0
-print("store mode ok")
-"""
-
-
-@pytest.mark.parametrize("mode", ["direct", "mixed"])
-def test_alternative_store_modes_give_the_same_results(mode) -> None:
-    """The epilogue's other store modes are selected per process by LC0B200_GEMM_STORE (measurement aids):
-    run them in a child process against the oracle, ragged edges and row pitch included."""
-    import os
-    import pathlib
-    import subprocess
-    import sys
-
-    root = str(pathlib.Path(__file__).resolve().parents[1])
-    env = dict(os.environ, LC0B200_GEMM_STORE=mode)
-    done = subprocess.run([sys.executable, "-c", _STORE_MODE_CHECK.format(root=root)], env=env, capture_output=True,
-                          text=True, timeout=300)
-    assert done.returncode == 0 and "store mode ok" in done.stdout, done.stdout + done.stderr
-
-
 def test_bf16_gemm_strided_output_and_f32_output(ops) -> None:
     from lczero_triton_b200 import _lib
 

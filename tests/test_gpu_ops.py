@@ -150,6 +150,20 @@ def test_add_bias_batched(ops, activation) -> None:
     _close(out, O.add_bias_batched(x, bias, activation))
 
 
+@pytest.mark.parametrize(("m", "k", "widths"), [(5, 24, (11, 13, 9)), (70, 7, (11, 13, 9)), (300, 1024, (1024, 1024, 1024)),
+                                               (8192, 1024, (1024, 1024, 1024))])
+def test_fused_qkv_projection_matches_three_matmuls(ops, m, k, widths) -> None:
+    """fused_qkv.py:30-123: three projections of one input with separate weights, widths and outputs
+    (the reference's test uses widths 11 / 13 / 9, tests/test_fused_qkv.py:36-75)."""
+    a = _bf(torch.randn((m, k), generator=_gen(140)) * 0.5)
+    ws = [_bf(torch.randn((k, n), generator=_gen(141 + i)) * 0.5) for i, n in enumerate(widths)]
+    outs = [torch.full((m, n), 7.0, dtype=BF16, device="cuda") for n in widths]
+    ops.fused_qkv_projection(outs[0], outs[1], outs[2], _dev(a), *[_dev(w) for w in ws], m, *widths, k)
+    atol = 0.25 * (k ** 0.5) * 2 ** -8 * 2 + 1e-3
+    for out, w in zip(outs, ws):
+        _close(out, O.matmul(a, w), rtol=8e-3, atol=atol)
+
+
 def test_fused_qkv_bias_with_three_widths(ops) -> None:
     rows = 9
     tensors = [_bf(torch.randn((rows, w), generator=_gen(20 + i))) for i, w in enumerate((11, 13, 9))]
@@ -300,7 +314,10 @@ def test_softmax_in_place_and_shift_invariance(ops) -> None:
     _close(base, torch.softmax(logits.float(), dim=1), rtol=RTOL, atol=2e-3)
 
 
-@pytest.mark.parametrize(("batch", "heads"), [(1, 4), (2, 32), (3, 24), (64, 32)])
+# Even head counts run the tcgen05 kernel (pairs of heads); odd head counts run the mma.sync kernel,
+# at each of its three heads-per-CTA settings (4, 8, 16: chosen from batch x heads against the SM count).
+@pytest.mark.parametrize(("batch", "heads"), [(1, 4), (2, 32), (3, 24), (64, 32), (2, 3), (7, 5), (3, 31),
+                                              (800, 31), (2600, 31)])
 def test_fused_attention_matches_three_step_oracle(ops, batch, heads) -> None:
     d = heads * 32
     q, k, v = (_bf(torch.randn((batch, 64, d), generator=_gen(60 + i))) for i in range(3))
@@ -367,6 +384,36 @@ def test_fused_attention_rows_at_the_edges_of_the_clamp_range(ops) -> None:
     torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got[0, 4, :32], v.float()[0, 9, :32], rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(got[0, 8, 64:96], v.float()[0, 3, 64:96], rtol=1e-2, atol=1e-2)
+
+
+def test_fused_attention_non_finite_value_rows(ops) -> None:
+    """A non-finite element of V.  The reference multiplies each head's probabilities by that head's V
+    only (batched_matmul.py:150-210), so the damage stays inside the head: the mma.sync kernel (odd head
+    count) must match the oracle exactly in where the NaNs are.  The tcgen05 kernel stacks two heads
+    into one 128-row product with zero off-diagonal probability blocks, and 0 x inf = NaN also reaches
+    the OTHER head of the pair (heads 2j and 2j+1) - the documented deviation; heads outside the pair
+    stay clean."""
+    batch, d_head = 2, 32
+    for heads in (3, 4):
+        d = heads * d_head
+        q, k, v = (_bf(torch.randn((batch, 64, d), generator=_gen(85 + i))) for i in range(3))
+        v[1, 17, 1 * d_head + 5] = float("inf")  # head 1 of position 1
+        bias = _bf(torch.randn((batch, heads, 64, 64), generator=_gen(88)) * 0.5)
+        out = torch.empty((batch, 64, d), dtype=BF16, device="cuda")
+        ops.attention(out, _dev(q), _dev(k), _dev(v), _dev(bias), 0.2, batch, heads)
+        want = O.attention_v(O.softmax_64(O.body_qk(q, k, 0.2, heads), bias), v)
+        got = out.float().cpu()
+        assert not torch.isfinite(want[1, :, d_head + 5]).any()      # the oracle: that output column of head 1
+        assert torch.isfinite(want[1, :, :d_head]).all()
+        clean = torch.ones_like(want, dtype=torch.bool)
+        clean[1, :, d_head:2 * d_head] = False                         # head 1 itself
+        if heads % 2 == 0:
+            clean[1, :, :d_head] = False                               # its pair partner (tcgen05 kernel only)
+            assert not torch.isfinite(got[1, :, d_head + 5]).any()
+        else:
+            assert torch.equal(torch.isfinite(got), torch.isfinite(want))
+        assert torch.isfinite(got[clean]).all()
+        torch.testing.assert_close(got[clean], want[clean], rtol=2e-2, atol=2e-2)
 
 
 # ------------------------------------------------------------------ batched matmuls
@@ -458,10 +505,12 @@ def test_output_probabilities_over_legal_moves(ops) -> None:
     wdl = torch.randn((batch, 3), generator=_gen(91))
     legal = (torch.rand((batch, 1858), generator=_gen(92)) < 0.02).to(torch.uint8)
     legal[3] = 0  # a position without legal moves
-    policy, wdl_probs = ops.output_probabilities(logits.cuda(), wdl.cuda(), legal.cuda())
-    want_policy, want_wdl = O.output_probabilities(logits, wdl, legal)
+    policy, wdl_probs, q_d = ops.output_probabilities(logits.cuda(), wdl.cuda(), legal.cuda())
+    want_policy, want_wdl, want_q_d = O.output_probabilities(logits, wdl, legal)
     torch.testing.assert_close(policy.cpu(), want_policy, rtol=1e-5, atol=1e-7)
     torch.testing.assert_close(wdl_probs.cpu(), want_wdl, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(q_d.cpu(), want_q_d, rtol=1e-5, atol=1e-6)
+    assert (q_d[:, 0].abs() <= 1).all() and torch.allclose(q_d[:, 1].cpu(), want_wdl[:, 1])
     assert policy[3].abs().sum() == 0 and (policy.cpu()[legal == 0] == 0).all()
-    everything, _ = ops.output_probabilities(logits.cuda(), wdl.cuda(), None)
+    everything, _, _ = ops.output_probabilities(logits.cuda(), wdl.cuda(), None)
     torch.testing.assert_close(everything.cpu(), torch.softmax(logits, dim=-1), rtol=1e-5, atol=1e-7)

@@ -1,6 +1,8 @@
-"""Host-side logic of the multi-GPU path on CPU: positions shard into disjoint contiguous ranges,
-ranks agree on a max-over-ranks time through a gloo group, and stitching the shards back gives
-the unsharded result (positions are independent).  World size 2, spawned as child processes."""
+"""The multi-GPU path.  On CPU: positions shard into disjoint contiguous ranges; ``ShardedNet`` (one
+process, one replica and one thread per device) splits a batch, runs its replicas and stitches the
+results in position order, shown with stand-in replicas; two gloo ranks (child processes) agree on a
+max-over-ranks time and reproduce the unsharded result.  On two GPUs: ``ShardedNet`` over both devices
+gives, bit for bit, what one GPU gives for the whole batch."""
 
 from __future__ import annotations
 
@@ -12,7 +14,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from lczero_triton_b200.sharding import shard_range
+from lczero_triton_b200.sharded import ShardedNet, shard_range
 from oracle import bt4_oracle as O
 
 
@@ -77,3 +79,88 @@ def test_two_ranks_reproduce_the_unsharded_result(tmp_path) -> None:
     policy, wdl, _ = O.forward(random_weights(TINY, 0), TINY, masks, values, table=table)
     torch.testing.assert_close(torch.cat([p["policy"] for p in parts]), policy, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(torch.cat([p["wdl"] for p in parts]), wdl, rtol=1e-5, atol=1e-6)
+
+
+class _FakeReplica:
+    """Stands in for a network replica on the CPU: every output row is a function of its own input row."""
+
+    calls: list[tuple[str, int]] = []
+
+    def __init__(self, weights, cfg, max_batch, device, mode) -> None:
+        self.max_batch, self.device = max_batch, device
+
+    def forward(self, masks: torch.Tensor, values: torch.Tensor):
+        assert masks.shape[0] <= self.max_batch
+        _FakeReplica.calls.append((str(self.device), masks.shape[0]))
+        key = (masks.sum(dim=1) % 1000).float()[:, None] + values.sum(dim=1, keepdim=True)
+        return key.expand(-1, 1858).contiguous(), key.expand(-1, 3) * 2.0, key * 3.0
+
+
+@pytest.mark.parametrize(("batch", "world"), [(7, 2), (64, 3), (2, 4), (1, 1)])
+def test_sharded_net_splits_and_stitches_in_position_order(batch, world) -> None:
+    from lczero_triton_b200.config import TINY
+    from lczero_triton_b200.synthetic import synthetic_planes
+
+    _FakeReplica.calls = []
+    net = ShardedNet({}, TINY, max_batch=64, devices=["cpu"] * world, replica_factory=_FakeReplica)
+    masks, values = synthetic_planes(batch, 5)
+    policy, wdl, mlh = net.forward(masks, values)
+    want = _FakeReplica({}, TINY, 64, "cpu", "bf16").forward(masks, values)
+    assert torch.equal(policy, want[0]) and torch.equal(wdl, want[1]) and torch.equal(mlh, want[2])
+    sizes = sorted(n for _, n in _FakeReplica.calls[:-1])
+    assert sum(sizes) == batch and len(sizes) == min(batch, world)  # empty shards launch nothing
+    assert max(sizes) - min(sizes) <= 1 or len(sizes) < world
+    net.close()
+
+
+def test_sharded_net_reports_a_failing_replica_and_bad_inputs() -> None:
+    from lczero_triton_b200.config import TINY
+    from lczero_triton_b200.synthetic import synthetic_planes
+
+    class Failing(_FakeReplica):
+        def forward(self, masks, values):
+            raise RuntimeError("replica lost")
+
+    masks, values = synthetic_planes(4, 0)
+    net = ShardedNet({}, TINY, max_batch=4, devices=["cpu", "cpu"], replica_factory=Failing)
+    with pytest.raises(RuntimeError, match="replica lost"):
+        net.forward(masks, values)
+    net.close()
+    net = ShardedNet({}, TINY, max_batch=2, devices=["cpu"], replica_factory=_FakeReplica)
+    with pytest.raises(ValueError):
+        net.forward(masks, values)            # batch above max_batch
+    with pytest.raises(ValueError):
+        net.forward(masks[:2].int(), values[:2])
+    net.close()
+    with pytest.raises(ValueError):
+        ShardedNet({}, TINY, max_batch=2, devices=[], replica_factory=_FakeReplica)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["bf16", "int8"])
+def test_two_gpus_in_one_process_equal_one_gpu(mode) -> None:
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    from lczero_triton_b200 import _lib, build
+    from lczero_triton_b200.config import TINY
+    from lczero_triton_b200.native import NativeNet
+    from lczero_triton_b200.synthetic import synthetic_planes
+    from lczero_triton_b200.weights import random_weights
+
+    build.build()
+    weights = random_weights(TINY, 4)
+    masks, values = synthetic_planes(37, 4)
+    both = ShardedNet(weights, TINY, max_batch=64, devices=[0, 1], mode=mode)
+    got = [x.clone() for x in both.forward(masks.pin_memory(), values.pin_memory())]
+    again = [x.clone() for x in both.forward(masks, values)]
+    both.close()
+    with torch.cuda.device(0):
+        one = NativeNet(weights, TINY, 64, device="cuda:0", mode=mode)
+        want = [x.cpu() for x in one.forward(masks.cuda(0), values.cuda(0))]
+        one.close()
+    for g, a, w in zip(got, again, want):
+        assert torch.equal(g, a) and torch.equal(g, w)
+    for device in (0, 1):  # the status words are per device: neither GPU saw a wait run out
+        with torch.cuda.device(device):
+            status, detail = _lib.device_status()
+            assert status == 0, (device, detail)
