@@ -9,7 +9,12 @@ N(0, 0.02) random-init weights of the BT4 shape; the trained network and lc0's b
 positions are not available offline).  Positions are independent, so N GPUs run N replicas
 on disjoint batches with no collective on the data path ("weak" scaling: the per-GPU batch
 is fixed); torch.distributed (NCCL) is used only for the barrier and the max-over-ranks of
-the device-side time.  Rank 0 prints one JSON line.
+the device-side time.  Rank 0 prints one JSON line: the bf16 batch-4096 headline with its `roofline`,
+`cpu_baseline`, `e2e`, `parity_sample` (a few positions of the benchmarked batch against the CPU oracle)
+and, as extra keys, the other figures the metric names: `int8` (same forward on int8 GEMMs, with the int8
+tensor peak measured in the same run), `batch1024`, `bt3_b256`, `attention_sweep`, `latency_batch64` and,
+for N > 1, `strong` (one global batch of 4096 / 1024 positions split over the ranks).  `--gpus N` without
+a multi-process launcher drives the N GPUs from one process (`ShardedNet`).
 """
 
 from __future__ import annotations
@@ -32,12 +37,6 @@ if str(ROOT) not in sys.path:
 
 METRIC = "positions/sec at BT4 shape"
 CPU_SAMPLE_BATCH = 8
-
-
-# int8 tensor-core throughput measured on this pool the same way as the bf16 figures (the library GEMM,
-# torch._int_mm at 8192^3: 20 launches for the burst figure, 2000 back to back for the sustained one).
-INT8_TOPS_BURST = 2754.5
-INT8_TOPS_SUSTAINED = 2439.5
 
 
 def _peaks() -> tuple[dict, str]:
@@ -200,11 +199,203 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _graph_step(fn):
+    """`fn` captured into a CUDA graph (returns the replay callable), or `fn` itself when capture fails."""
+    try:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        return graph.replay, None
+    except Exception as exc:  # noqa: BLE001 - fall back to eager launches, say so in the line
+        return fn, repr(exc)[:160]
+
+
+def _forward_rate(net, masks_d, values_d, batch: int, world: int, args, dist, *, graph: bool = True) -> dict:
+    """Device-resident positions/s of `net` on one batch: whole-job value, max over ranks."""
+    def eager() -> None:
+        net.forward(masks_d, values_d)
+
+    eager()
+    step, error = _graph_step(eager) if graph else (eager, None)
+    total_ms = _timed_steps(step, args.warmup, args.steps, dist)
+    out = {"value": world * batch * args.steps / (total_ms * 1e-3), "unit": "positions/s",
+           "ms_per_step": total_ms / args.steps, "batch_per_gpu": batch,
+           "launch": "CUDA graph replay" if graph and error is None else "eager launches"}
+    if error is not None:
+        out["graph_error"] = error
+    return out
+
+
+def _e2e_rate(net, masks_h, values_h, batch: int, world: int, args, dist) -> dict:
+    """The same metric through the public API with HOST buffers: every step copies the packed planes
+    from pinned memory to the device, runs the forward and copies policy / WDL / moves-left back."""
+    from lczero_triton_b200.config import POLICY_SIZE
+
+    out_h = [torch.empty((batch, POLICY_SIZE), dtype=torch.float32).pin_memory(),
+             torch.empty((batch, 3), dtype=torch.float32).pin_memory(),
+             torch.empty((batch, 1), dtype=torch.float32).pin_memory()]
+    masks_in = torch.empty(masks_h.shape, dtype=masks_h.dtype, device="cuda")
+    values_in = torch.empty(values_h.shape, dtype=values_h.dtype, device="cuda")
+
+    def step() -> None:
+        masks_in.copy_(masks_h, non_blocking=True)
+        values_in.copy_(values_h, non_blocking=True)
+        outs = net.forward(masks_in, values_in)
+        for dst, src in zip(out_h, outs):
+            dst.copy_(src, non_blocking=True)
+
+    ms = _timed_steps(step, max(1, args.warmup // 2), args.steps, dist)
+    return {"value": world * batch * args.steps / (ms * 1e-3), "unit": "positions/s",
+            "h2d_bytes_per_step": masks_h.numel() * 8 + values_h.numel() * 4,
+            "d2h_bytes_per_step": sum(t.numel() * 4 for t in out_h), "ms_per_step": ms / args.steps}
+
+
+def _int8_peak() -> dict:
+    """int8 tensor-core throughput of this GPU, measured the way the bf16 figures of MEASURED_PEAKS.json
+    were: the library GEMM (torch._int_mm) at 8192^3, best of 10 single launches (burst) and launched back
+    to back for about two seconds (sustained, under the power cap)."""
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+    ops_per_call = 2.0 * n ** 3
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = float("inf")
+    for _ in range(10):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        torch._int_mm(a, b)
+        e.record()
+        e.synchronize()
+        best = min(best, s.elapsed_time(e))
+    calls = max(50, int(2000.0 / best))
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(calls):
+        torch._int_mm(a, b)
+    e.record()
+    e.synchronize()
+    sustained_ms = s.elapsed_time(e) / calls
+    return {"int8_tops": ops_per_call / best / 1e9, "int8_tops_sustained": ops_per_call / sustained_ms / 1e9,
+            "how": f"torch._int_mm {n}^3: best of 10 (burst), {calls} back to back (sustained)"}
+
+
+# DRAM traffic of the QKV GEMM per row of A: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture
+# of a launch at 131072 rows (A 268 MB + C 805 MB, more than eight times the L2), divided by the rows.
+QKV_TRAFFIC_BYTES_PER_ROW = {"bf16": 7943.0, "int8": 6714.0}
+
+
+def _qkv_roofline(net, cfg, batch: int, mode: str, peaks: dict, peak_kind: str, int8_peak: dict | None) -> dict:
+    """The dominant kernel, timed alone in the form the forward pass launches it: the QKV projection
+    GEMM (bf16: LayerNorm of the input rows folded into the epilogue; int8: dequantising epilogue)."""
+    from lczero_triton_b200 import ops
+
+    t_rows = batch * 64
+    if mode == "int8":
+        layer = net.layers[0]["qkv"]
+        a = torch.randint(-127, 128, (t_rows, cfg.embedding), device="cuda", dtype=torch.int8)
+        extra = {"bias": layer.bias, "col_scale": layer.col_scale,
+                 "row_scale": torch.rand(t_rows, device="cuda") * 0.01 + 0.001}
+        kernel_name = "gemm_tcgen05_kernel<256, int8, NK, pair, plain>"
+    else:
+        layer = net.layers[0]["qkv_f"] if net.deferred else net.layers[0]["qkv"]
+        a = torch.randn((t_rows, cfg.embedding), device="cuda").to(torch.bfloat16)
+        if net.deferred:
+            parts = (cfg.embedding + 63) // 64
+            stats = torch.rand((parts, t_rows, 2), device="cuda") + 1.0
+            extra = {"ln_in": (stats, layer.fold_c, layer.fold_d)}
+            kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, ln_in>"
+        else:
+            extra = {"bias": layer.bias}
+            kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, plain>"
+    out = torch.empty((t_rows, layer.n), dtype=torch.bfloat16, device="cuda")
+
+    def gemm_once() -> None:
+        ops.gemm(out, a, layer.w, m=t_rows, n=layer.n, k=layer.k, w_layout=layer.layout, **extra)
+
+    gemm_ms = _timed_steps(gemm_once, 3, 10, None) / 10
+    gemm_flops = 2.0 * t_rows * layer.n * layer.k
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    if mode == "int8":
+        peak, sustained = int8_peak["int8_tops"], int8_peak["int8_tops_sustained"]
+        peak_source = "measured in this run: " + int8_peak["how"]
+    else:
+        peak, sustained = peaks["bf16_tflops"], peaks["bf16_tflops_sustained"]
+        peak_source = f"{peak_kind} burst bf16"
+    eb = 1 if mode == "int8" else 2
+    algorithmic = float(t_rows * layer.k * eb + layer.n * layer.k * eb + t_rows * layer.n * 2)
+    per_row = QKV_TRAFFIC_BYTES_PER_ROW[mode]
+    traffic = per_row * t_rows if per_row is not None else None
+    return {
+        "bound": "tensor", "kernel": "%s (QKV projection, M=%d N=%d K=%d)" % (kernel_name, t_rows, layer.n, layer.k),
+        "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if mode == "bf16" else "TOP/s", "frac": achieved / peak,
+        "peak_source": peak_source, "frac_of_sustained_peak": achieved / sustained,
+        "ms_per_launch": gemm_ms, "flops_per_launch": gemm_flops, "algorithmic_bytes": algorithmic,
+        "traffic": traffic, "traffic_over_algorithmic": None if traffic is None else traffic / algorithmic,
+        "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 131072 rows, scaled by rows",
+    }
+
+
+def _attention_sweep(peaks: dict, peak_kind: str) -> list[dict]:
+    """The stand-alone edge-biased attention operator at B = 64 / 512 / 4096 (32 heads of depth 32)."""
+    from lczero_triton_b200 import ops
+
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    # tensor-pipe share of the kernel's cycles: ncu sm__pipe_tensor_cycles_active of the B = 512 capture
+    tensor_pipe_pct = {512: 10.4}
+    rows = []
+    for b in (64, 512, 4096):
+        h, d = 32, 1024
+        q, k_, v = (torch.randn((b, 64, d), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(3))
+        bias = (torch.randn((b, h, 64, 64), generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        out = torch.empty((b, 64, d), dtype=torch.bfloat16, device="cuda")
+
+        def once() -> None:
+            ops.attention(out, q, k_, v, bias, 32 ** -0.5, b, h)
+
+        ms = _timed_steps(once, 3, 20, None) / 20
+        nbytes = 786432.0 * b
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        rows.append({"batch": b, "ms": ms, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
+                     "peak_source": f"{peak_kind} HBM copy", "tflops": 4.0 * b * h * 64 * 64 * 32 / (ms * 1e-3) / 1e12,
+                     "tensor_pipe_pct_ncu": tensor_pipe_pct.get(b),
+                     "working_set": "larger than L2" if nbytes > 126e6 else "fits in L2: not an HBM figure"})
+    return rows
+
+
+def _parity_sample(net, masks_h, values_h, cfg, weights, mode: str, positions: int = 8) -> tuple[dict, float]:
+    """A few positions of the benchmarked batch, picked across it, against the fp32 CPU oracle.
+    Returns the report and the oracle's positions per second on that sample."""
+    from lczero_triton_b200 import mapping_table
+    from oracle import bt4_oracle
+
+    batch = masks_h.shape[0]
+    index = torch.linspace(0, batch - 1, positions).long().unique()
+    outs = net.forward(masks_h.cuda(), values_h.cuda())
+    got = [x[index.cuda()].float().cpu() for x in outs]
+    table = torch.tensor(mapping_table.values(), dtype=torch.int32)
+    t0 = time.perf_counter()
+    want = bt4_oracle.forward(weights, cfg, masks_h[index], values_h[index], table=table)
+    oracle_s = time.perf_counter() - t0
+    report = {"positions": [int(i) for i in index], "tolerance": "1e-2 absolute or 1 % relative (bf16 target)",
+              "oracle": "fp32 CPU forward", "oracle_seconds": oracle_s}
+    for name, g, w in zip(("policy", "wdl", "mlh"), got, want):
+        err = (g - w).abs()
+        outside = ~((err <= 1e-2) | (err <= 1e-2 * w.abs()))
+        report[name] = {"max_abs_err": float(err.max()), "outside_tolerance": int(outside.sum()), "count": g.numel(),
+                        "max_err_over_spread": float(err.max() / w.std().clamp_min(1e-12))}
+    if mode == "int8":
+        report["note"] = "int8 GEMMs: no end-to-end tolerance is promised; the figures are against the fp32 forward"
+    return report, float(len(index)) / oracle_s
+
+
 def run(args) -> None:
     rank, world, local, dist = _dist_setup(args.gpus)
     from lczero_triton_b200 import _lib, build
-    from lczero_triton_b200.config import BT4, INPUT_PLANES, POLICY_SIZE
+    from lczero_triton_b200.config import BT3, BT4
     from lczero_triton_b200.net import Bt4Net
+    from lczero_triton_b200.sharded import shard_range
     from lczero_triton_b200.synthetic import synthetic_planes
     from lczero_triton_b200.weights import random_weights
 
@@ -219,121 +410,85 @@ def run(args) -> None:
     masks_h, values_h = masks_h.pin_memory(), values_h.pin_memory()
     masks_d, values_d = masks_h.cuda(), values_h.cuda()
 
-    def step_eager() -> None:
-        net.forward(masks_d, values_d)
-
-    # ---- device-resident throughput
-    step_eager()
+    # ---- headline: device-resident throughput, then end to end with host buffers
+    net.forward(masks_d, values_d)
     torch.cuda.synchronize()
     launches_before = _lib.launch_count()
-    step_eager()
+    net.forward(masks_d, values_d)
     launches_per_step = _lib.launch_count() - launches_before
-    step_resident = step_eager
-    graph_error = None
-    if args.graph:
-        # The whole forward as one CUDA graph: the ~220 launches replay without host work in between.
-        try:
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                net.forward(masks_d, values_d)
-            step_resident = graph.replay
-        except Exception as exc:  # noqa: BLE001 - fall back to eager launches, say so in the line
-            args.graph = 0
-            graph_error = repr(exc)[:160]
     sampler = ClockSampler(local)
     sampler.start()
-    total_ms = _timed_steps(step_resident, args.warmup, args.steps, dist)
+    head = _forward_rate(net, masks_d, values_d, batch, world, args, dist, graph=bool(args.graph))
     clocks = sampler.stop()
-    ms_per_step = total_ms / args.steps
-    value = world * batch * args.steps / (total_ms * 1e-3)
-
-    # ---- end to end through the public API: pinned host inputs in, host results out, every step
-    out_h = [torch.empty((batch, POLICY_SIZE), dtype=torch.float32).pin_memory(),
-             torch.empty((batch, 3), dtype=torch.float32).pin_memory(),
-             torch.empty((batch, 1), dtype=torch.float32).pin_memory()]
-    masks_in, values_in = torch.empty_like(masks_d), torch.empty_like(values_d)
-
-    def step_e2e() -> None:
-        masks_in.copy_(masks_h, non_blocking=True)
-        values_in.copy_(values_h, non_blocking=True)
-        outs = net.forward(masks_in, values_in)
-        for dst, src in zip(out_h, outs):
-            dst.copy_(src, non_blocking=True)
-
-    e2e_ms = _timed_steps(step_e2e, max(1, args.warmup // 2), args.steps, dist)
-    e2e_value = world * batch * args.steps / (e2e_ms * 1e-3)
-    h2d = masks_h.numel() * 8 + values_h.numel() * 4
-    d2h = sum(t.numel() * 4 for t in out_h)
+    e2e = _e2e_rate(net, masks_h, values_h, batch, world, args, dist)
 
     line = {
-        "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": head["value"], "unit": "positions/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16" if args.mode == "bf16" else "int8", "data": "synthetic",
         "config": _config(batch, world, args.mode),
-        "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
-        "e2e": {"value": e2e_value, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+        "clocks": clocks, "gpu_launches": launches_per_step * args.steps, "e2e": e2e,
     }
-    line["config"]["launch"] = "CUDA graph replay" if args.graph else "eager launches"
-    if graph_error is not None:
-        line["config"]["graph_error"] = graph_error
+    line["config"]["launch"] = head["launch"]
+    if "graph_error" in head:
+        line["config"]["graph_error"] = head["graph_error"]
     flops = cfg.flops_per_position()
-    line["forward_tflops_per_gpu"] = flops * batch / (ms_per_step * 1e-3) / 1e12
+    line["forward_tflops_per_gpu"] = flops * batch / (head["ms_per_step"] * 1e-3) / 1e12
     line["forward_frac_of_sustained_bf16_peak"] = line["forward_tflops_per_gpu"] / peaks["bf16_tflops_sustained"]
 
+    extras = not args.headline_only
+    int8_peak = None
+    if extras and args.mode == "bf16":
+        # ---- the same forward with int8 GEMMs (weak scaling, every N), and its own peak
+        int8_peak = _int8_peak()
+        net8 = Bt4Net(weights, cfg, mode="int8", deferred_layer_norm=deferred)
+        row = _forward_rate(net8, masks_d, values_d, batch, world, args, dist)
+        row["e2e"] = _e2e_rate(net8, masks_h, values_h, batch, world, args, dist)
+        row["forward_tops_per_gpu"] = flops * batch / (row["ms_per_step"] * 1e-3) / 1e12
+        row["forward_frac_of_sustained_int8_peak"] = row["forward_tops_per_gpu"] / int8_peak["int8_tops_sustained"]
+        row["peak"] = int8_peak
+        if rank == 0 and world == 1:
+            row["roofline"] = _qkv_roofline(net8, cfg, batch, "int8", peaks, peak_kind, int8_peak)
+            row["parity_sample"], _ = _parity_sample(net8, masks_h, values_h, cfg, weights, "int8")
+        line["int8"] = row
+        del net8
+        torch.cuda.empty_cache()
+    if extras and world > 1:
+        # ---- strong scaling: ONE global batch split by position over the ranks (no collective on the path)
+        strong = {}
+        for global_batch in (4096, 1024):
+            lo, hi = shard_range(global_batch, rank, world)
+            m_all, v_all = synthetic_planes(global_batch, seed=2000)
+            m_d, v_d = m_all[lo:hi].cuda(), v_all[lo:hi].cuda()
+            row = _forward_rate(net, m_d, v_d, hi - lo, 1, args, dist)
+            strong[f"global_batch_{global_batch}"] = {
+                "value": global_batch / (row["ms_per_step"] * 1e-3), "unit": "positions/s",
+                "ms_per_step": row["ms_per_step"], "positions_per_gpu": hi - lo, "launch": row["launch"]}
+        line["strong"] = strong
+
     if rank == 0 and world == 1:
-        # ---- roofline of the dominant kernel: the QKV projection GEMM (tcgen05), timed alone, in the
-        # form the forward pass launches it (bf16: LayerNorm of the input rows folded into the epilogue)
-        from lczero_triton_b200 import ops
-
-        t_rows = batch * 64
-        if args.mode == "int8":
-            layer = net.layers[0]["qkv"]
-            a = torch.randint(-127, 128, (t_rows, cfg.embedding), device="cuda", dtype=torch.int8)
-            extra = {"bias": layer.bias, "col_scale": layer.col_scale,
-                     "row_scale": torch.rand(t_rows, device="cuda") * 0.01 + 0.001}
-            kernel_name = "gemm_tcgen05_kernel<256, int8, NK, pair, plain>"
-        else:
-            layer = net.layers[0]["qkv_f"] if net.deferred else net.layers[0]["qkv"]
-            a = torch.randn((t_rows, cfg.embedding), device="cuda").to(torch.bfloat16)
-            if net.deferred:
-                parts = (cfg.embedding + 63) // 64
-                stats = torch.rand((parts, t_rows, 2), device="cuda") + 1.0
-                extra = {"ln_in": (stats, layer.fold_c, layer.fold_d)}
-                kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, ln_in>"
-            else:
-                extra = {"bias": layer.bias}
-                kernel_name = "gemm_tcgen05_kernel<256, bf16, NK, pair, plain>"
-        out = torch.empty((t_rows, layer.n), dtype=torch.bfloat16, device="cuda")
-
-        def gemm_once() -> None:
-            ops.gemm(out, a, layer.w, m=t_rows, n=layer.n, k=layer.k, w_layout=layer.layout, **extra)
-
-        gemm_ms = _timed_steps(gemm_once, 3, 10, None) / 10
-        gemm_flops = 2.0 * t_rows * layer.n * layer.k
-        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
-        int8 = args.mode == "int8"
-        peak = INT8_TOPS_BURST if int8 else peaks["bf16_tflops"]
-        sustained = INT8_TOPS_SUSTAINED if int8 else peaks["bf16_tflops_sustained"]
-        # DRAM traffic of this kernel from one ncu capture at 32768 rows (profiles/gemm_tcgen05_*_m32768.md),
-        # scaled by the row count: the traffic is A + C, both proportional to the rows.
-        traffic_per_row = (225.25e6 if args.mode == "bf16" else 178.33e6) / 32768.0
-        line["roofline"] = {
-            "bound": "tensor", "kernel": "%s (QKV projection, M=%d N=%d K=%d)" % (kernel_name, t_rows, layer.n, layer.k),
-            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "peak_source": "measured burst int8 (library GEMM 8192^3)" if int8 else f"{peak_kind} burst bf16",
-            "frac_of_sustained_peak": achieved / sustained,
-            "ms_per_launch": gemm_ms, "flops_per_launch": gemm_flops,
-            "traffic": traffic_per_row * t_rows,
-            "traffic_source": "ncu dram__bytes_read+write at 32768 rows, scaled by rows",
-        }
-        # ---- CPU baseline beside it (bounded sample of the same workload)
+        line["roofline"] = _qkv_roofline(net, cfg, batch, args.mode, peaks, peak_kind, int8_peak or
+                                         (_int8_peak() if args.mode == "int8" else None))
+        # ---- parity of the benchmarked batch, and the CPU baseline from the same oracle run
+        parity, cpu_rate = _parity_sample(net, masks_h, values_h, cfg, weights, args.mode)
+        line["parity_sample"] = parity
         if not args.no_cpu_baseline:
             torch.set_num_threads(max(1, os.cpu_count() or 1))
             rate, ms = _cpu_forward_rate(cfg, CPU_SAMPLE_BATCH, 3, 1)
             line["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": torch.get_num_threads(),
                                     "kind": "port", "sample": f"BT4 fp32 forward, batch {CPU_SAMPLE_BATCH}, median of 3 after 1 warm-up ({ms:.0f} ms each)"}
+        if extras:
+            # ---- the other configurations the metric names
+            m1k, v1k = synthetic_planes(1024, seed=3000)
+            line["batch1024"] = _forward_rate(net, m1k.cuda(), v1k.cuda(), 1024, 1, args, None)
+            net3 = Bt4Net(random_weights(BT3, 0), BT3, mode="bf16", deferred_layer_norm=deferred)
+            m256, v256 = synthetic_planes(256, seed=3001)
+            row = _forward_rate(net3, m256.cuda(), v256.cuda(), 256, 1, args, None)
+            row["workload"] = "BT3-shape forward (E768 L15 H24 F1024), batch 256"
+            row["forward_tflops"] = BT3.flops_per_position() * 256 / (row["ms_per_step"] * 1e-3) / 1e12
+            line["bt3_b256"] = row
+            del net3
+            line["attention_sweep"] = _attention_sweep(peaks, peak_kind)
         # ---- p50 latency at batch 64 (whole forward replayed from a CUDA graph)
         if not args.no_latency:
             try:
@@ -366,6 +521,63 @@ def run(args) -> None:
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_one_process(args) -> None:
+    """`--gpus N` without a multi-process launcher: ONE process drives N GPUs through `ShardedNet` (a
+    replica and a worker thread per device).  A global batch of N x `--batch` host-resident positions is
+    split by position every step, so the H2D / D2H copies are inside the timed region and `value` is the
+    end-to-end figure.  Timed with CUDA events on every device's stream; the slowest device counts."""
+    from lczero_triton_b200 import build
+    from lczero_triton_b200.config import BT4
+    from lczero_triton_b200.sharded import ShardedNet
+    from lczero_triton_b200.synthetic import synthetic_planes
+    from lczero_triton_b200.weights import random_weights
+
+    build.build()
+    n = args.gpus
+    if torch.cuda.device_count() < n:
+        raise SystemExit(f"--gpus {n}: only {torch.cuda.device_count()} CUDA devices are visible")
+    total = n * args.batch
+    net = ShardedNet(random_weights(BT4, 0), BT4, max_batch=total, devices=list(range(n)), mode=args.mode)
+    masks_h, values_h = synthetic_planes(total, seed=1000)
+    masks_h, values_h = masks_h.pin_memory(), values_h.pin_memory()
+    for _ in range(args.warmup):
+        net.forward(masks_h, values_h)
+    events = []
+    for d in range(n):
+        with torch.cuda.device(d):
+            torch.cuda.synchronize()
+            events.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+    sampler = ClockSampler(0)
+    sampler.start()
+    for d in range(n):
+        with torch.cuda.device(d):
+            events[d][0].record()
+    for _ in range(args.steps):
+        net.forward(masks_h, values_h)
+    elapsed = []
+    for d in range(n):
+        with torch.cuda.device(d):
+            events[d][1].record()
+            torch.cuda.synchronize()
+            elapsed.append(events[d][0].elapsed_time(events[d][1]))
+    clocks = sampler.stop()
+    ms = max(elapsed)
+    value = total * args.steps / (ms * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "positions/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.mode == "bf16" else "int8", "data": "synthetic",
+        "config": dict(_config(args.batch, n, args.mode), parallelism=f"one process, {n} replica threads (ShardedNet)",
+                       launch="eager launches, host buffers in and out every step"),
+        "clocks": clocks, "gpu_launches": 185 * n * args.steps,
+        "e2e": {"value": value, "unit": "positions/s", "h2d_bytes_per_step": masks_h.numel() * 8 + values_h.numel() * 4,
+                "d2h_bytes_per_step": total * (1858 + 3 + 1) * 4, "ms_per_step": ms / args.steps},
+        "per_device_ms": elapsed,
+    }
+    net.close()
+    print(json.dumps(line), flush=True)
 
 
 def run_kernel(args) -> None:
@@ -419,11 +631,11 @@ def run_kernel(args) -> None:
 
         ms = _timed_steps(once, 3, args.iters, None) / args.iters
         achieved = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-        peak = INT8_TOPS_BURST if int8 else peaks["bf16_tflops"]
+        peak = _int8_peak()["int8_tops"] if int8 else peaks["bf16_tflops"]
         eb = 1 if int8 else 2
         line.update({"shape": [m, n, k], "mode": args.mode, "layout": args.layout, "epilogue": args.epilogue,
                      "out": args.out, "ms": ms, "achieved": achieved, "unit": "TFLOP/s", "peak": peak,
-                     "frac": achieved / peak, "peak_source": "measured burst int8 (library GEMM 8192^3)" if int8 else f"{peak_kind} burst bf16",
+                     "frac": achieved / peak, "peak_source": "int8 burst measured in this run (torch._int_mm 8192^3)" if int8 else f"{peak_kind} burst bf16",
                      "algorithmic_bytes": m * k * eb + n * k * eb + m * n * out.element_size()})
     elif args.kernel in ("quantize", "normalize_quantize"):
         # int8 row quantisers: bf16 rows in, int8 rows and one f32 scale per row out
@@ -449,6 +661,35 @@ def run_kernel(args) -> None:
         line.update({"rows": rows, "width": width, "ms": ms, "achieved": achieved, "unit": "GB/s",
                      "peak": peaks["hbm_gbs"], "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy",
                      "algorithmic_bytes": nbytes})
+    elif args.kernel in ("policy_tail", "embed_concat"):
+        # the two HBM-bound ends of the forward: packed planes -> embedding input, records -> 1858 f32 logits
+        from lczero_triton_b200 import mapping_table
+        from lczero_triton_b200.synthetic import synthetic_planes
+
+        b = args.batch
+        if args.kernel == "embed_concat":
+            masks, values = (t.cuda() for t in synthetic_planes(b, 0))
+            position = torch.randn((b, 64 * 64), generator=gen, device="cuda").to(torch.bfloat16)
+            out = torch.empty((b * 64, 112 + 64), dtype=torch.bfloat16, device="cuda")
+
+            def once() -> None:
+                ops.embed_concat(out, masks, values, position, b, 64)
+            nbytes = b * (112 * 12.0 + 64 * 64 * 2.0 + 64 * 176 * 2.0)
+        else:
+            width = 1024
+            records = torch.randn((b, 4288), generator=gen, device="cuda").to(torch.bfloat16)
+            keys = torch.randn((b * 64, width), generator=gen, device="cuda").to(torch.bfloat16)
+            w = torch.randn((width, 4), generator=gen, device="cuda").to(torch.bfloat16)
+            table = torch.tensor(mapping_table.values(), dtype=torch.int32, device="cuda")
+            out = torch.empty((b, 1858), dtype=torch.float32, device="cuda")
+
+            def once() -> None:
+                ops.policy_tail(out, records, keys, w, table, b, width)
+            nbytes = b * (4288 * 2.0 + 8 * width * 2.0 + 1858 * 4.0)  # records, the eight promotion-rank key rows, logits
+        ms = _timed_steps(once, 3, args.iters, None) / args.iters
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        line.update({"batch": b, "ms": ms, "achieved": achieved, "unit": "GB/s", "peak": peaks["hbm_gbs"],
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy", "algorithmic_bytes": nbytes})
     elif args.kernel == "attention":
         b, h, d = args.batch, 32, 1024
         q, k_, v = (torch.randn((b, 64, d), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(3))
@@ -497,10 +738,12 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the extra keys (int8, batch 1024, BT3, attention sweep, strong scaling)")
     ap.add_argument("--graph", type=int, default=1, help="replay the forward from a CUDA graph in the timed loop")
     ap.add_argument("--deferred-ln", type=int, default=-1,
                     help="LayerNorm folded into the GEMM epilogues: 1 / 0, or -1 for the mode's default")
-    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm", "quantize", "normalize_quantize"],
+    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "layer_norm", "quantize", "normalize_quantize", "policy_tail", "embed_concat"],
                     help="measure one kernel instead of the whole forward pass")
     ap.add_argument("--m", type=int, default=262144)
     ap.add_argument("--n", type=int, default=3072)
@@ -519,6 +762,8 @@ def main() -> None:
         return
     if args.impl == "reference":
         run_reference(args)
+    elif args.gpus > 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_one_process(args)
     else:
         run(args)
 

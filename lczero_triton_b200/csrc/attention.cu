@@ -240,9 +240,9 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
   cp_async_wait<0>();
 }
 
-// softmax_64.py:45-71, one warp per row of 64, two columns per lane.
-__global__ void __launch_bounds__(256) softmax_64_kernel(bf16* out, const bf16* qk, const bf16* smolgen,
-                                                         long long rows) {
+// softmax_64.py:45-71, one warp per row of 64, two columns per lane.  (A device function: the kernel
+// below and the pointer-only entry points generated by lc0ex_bridge.py both wrap it.)
+__device__ __forceinline__ void softmax_64_body(bf16* out, const bf16* qk, const bf16* smolgen, long long rows) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -258,6 +258,11 @@ __global__ void __launch_bounds__(256) softmax_64_kernel(bf16* out, const bf16* 
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
   const float inv = 1.0f / sum;
   reinterpret_cast<uint32_t*>(out + row * 64)[lane] = pack_bf16x2(e0 * inv, e1 * inv);
+}
+
+__global__ void __launch_bounds__(256) softmax_64_kernel(bf16* out, const bf16* qk, const bf16* smolgen,
+                                                         long long rows) {
+  softmax_64_body(out, qk, smolgen, rows);
 }
 
 // Tensor-core QK^T for 64 x 64 outputs with any K that is a multiple of 32: body_qk (heads

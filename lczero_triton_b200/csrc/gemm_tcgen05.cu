@@ -257,6 +257,15 @@ __device__ __forceinline__ void mish32(float (&y)[32]) {
 template <int MODE, bool INT8, int BN>
 __device__ __forceinline__ void finish32_sv(const uint32_t* v, uint32_t* packed, const uint32_t* skip, const RowCtx& r,
                                             const KernelParams& p, float& sum, float& sumsq, uint32_t vec, int tcol) {
+  if (MODE == kPlain && !INT8) {
+    // A bf16 product with neither bias nor activation (the smolgen shared projection: K = 256, one
+    // gigabyte of output per layer at batch 4096) is all epilogue: round and pack, nothing else.
+    if (p.bias == nullptr && p.activation == LC0B200_ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+      return;
+    }
+  }
   float y[32];
 #pragma unroll
   for (int g = 0; g < 4; ++g) {

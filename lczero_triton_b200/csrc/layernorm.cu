@@ -54,9 +54,10 @@ struct LnParams {
   float epsilon;
 };
 
-// One warp per row; GROUPS = ceil(width / 256) register groups per lane.
+// One warp per row; GROUPS = ceil(width / 256) register groups per lane.  The body is a device function
+// so that a pointer-only entry point with baked shapes can wrap it too (lc0ex_bridge.py).
 template <int GROUPS>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(const LnParams p) {
+__device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kWarpsPerBlock) + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -147,6 +148,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(co
       }
     }
   }
+}
+
+template <int GROUPS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(const LnParams p) {
+  layer_norm_warp_body<GROUPS>(p);
 }
 
 // One CTA per row, row cached in shared memory as fp32 (any width, any alignment).

@@ -1,0 +1,279 @@
+"""The lc0ex bridge: the linker's plan (dependencies, buffer packing) and the kernel artifacts.
+
+The linker cases restate the behaviours the reference pins for its own linker
+(packages/lc0ex/tests/test_builder.py:42-192, packages/lc0ex/tests/test_kernel_builder.py:59-197) against
+``lczero_triton_b200.lc0ex_bridge``: same declarations in, same sizes, offsets and dependency lists out.
+The artifact cases compile real pointer-only entry points for sm_100a (nvcc needs no GPU) and, on a GPU,
+launch them the way an lc0ex runtime does - module load, symbol lookup, a static grid and nothing but
+pointers - and check the results against the CPU oracle.
+"""
+
+from __future__ import annotations
+
+import json
+
+import pytest
+import torch
+
+from lczero_triton_b200 import lc0ex_bridge as B
+from oracle import bt4_oracle as O
+
+F16, F32, U8, U64, BF16 = B.DataType.F16, B.DataType.F32, B.DataType.U8, B.DataType.U64, B.DataType.BF16
+POINTER, NULL_POINTER = B.ParameterType.POINTER, B.ParameterType.NULL_POINTER
+
+
+def _builder() -> B.ExecutableBuilder:
+    return B.ExecutableBuilder().set_target(B.Vendor.NVIDIA, "sm_100a")
+
+
+def _artifact(*, function: str = "kernel", parameters=(POINTER,)) -> B.KernelArtifact:
+    return B.KernelArtifact(B.BinaryFormat.CUBIN, b"fake cubin", function, tuple(parameters), (2, 3, 1), (128, 1, 1), 256)
+
+
+def _external(builder: B.ExecutableBuilder, name: str, *, writable: bool = False) -> B.Buffer:
+    return builder.persistent_buffer(name=name, shape=(1,), dtype=F16, writable=writable)
+
+
+# ------------------------------------------------------------------ buffers and packing
+
+def test_buffer_is_an_opaque_storage_identity() -> None:
+    buffer = B.Buffer()
+    assert not hasattr(buffer, "shape") and not hasattr(buffer, "dtype") and not hasattr(buffer, "reshape")
+
+
+def test_persistent_buffer_is_packed_into_the_executable_allocation() -> None:
+    builder = _builder()
+    result = builder.persistent_buffer(name="weights", shape=(2, 3), dtype=F16, alignment_bytes=16)
+    executable = builder.build()
+    assert isinstance(result, B.Buffer)
+    assert (executable.persistent_allocation.size_bytes, executable.persistent_allocation.alignment_bytes) == (12, 16)
+    first = executable.buffers[0]
+    assert (first.name, first.offset, first.shape, first.data_type) == ("weights", 0, (2, 3), F16)
+
+
+def test_a_name_is_one_buffer_within_its_scope_and_private_to_programs() -> None:
+    builder = _builder()
+    assert builder.persistent_buffer(name="w", shape=(2, 3), dtype=F16) is builder.persistent_buffer(name="w", shape=(2, 3), dtype=F16)
+    first, second = builder.program(name="batch-1"), builder.program(name="batch-2")
+    first.buffer(name="input", shape=(1,), dtype=F16)
+    second.buffer(name="input", shape=(2,), dtype=F16)
+    executable = builder.build()
+    assert [p.name for p in executable.programs] == ["batch-1", "batch-2"]
+    assert executable.programs[0].buffers[0].shape == (1,) and executable.programs[1].buffers[0].shape == (2,)
+
+
+def test_unused_temporaries_do_not_force_an_allocation_and_used_ones_are_packed() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    program.temporary_buffer(size_bytes=128, alignment_bytes=64)
+    assert builder.build().programs[0].execution_allocation is None
+    first = program.temporary_buffer(size_bytes=64, alignment_bytes=32)
+    second = program.temporary_buffer(size_bytes=64, alignment_bytes=32)
+    kernel = builder.add_kernel(_artifact())
+    program.call(kernel, first)
+    program.call(kernel, second)
+    assert builder.build().programs[0].execution_allocation.size_bytes == 128  # unordered: no sharing
+
+
+def test_named_execution_buffers_keep_their_order_and_alignment() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    program.buffer(name="input", shape=(2,), dtype=F16, alignment_bytes=16)
+    program.buffer(name="output", shape=(2,), dtype=F16, writable=True, alignment_bytes=16)
+    main = builder.build().programs[0]
+    assert main.execution_allocation.size_bytes == 20
+    assert [(b.name, b.offset) for b in main.buffers] == [("input", 0), ("output", 16)]
+
+
+@pytest.mark.parametrize(("dtype", "size"), [(F32, 4), (U8, 1), (F16, 2), (U64, 8), (BF16, 2)])
+def test_data_type_sizes(dtype, size) -> None:
+    assert B.data_type_size_bytes(dtype) == size
+
+
+def test_unknown_dtype_is_rejected_at_declaration() -> None:
+    with pytest.raises(KeyError):
+        _builder().persistent_buffer(name="unknown", shape=(1,), dtype=B.DataType.UNKNOWN)
+
+
+def test_metadata_and_target_survive_the_written_form(tmp_path) -> None:
+    builder = _builder().set_metadata(b"fingerprint")
+    builder.build_and_write(tmp_path / "net.lc0ex.json")
+    restored = json.loads((tmp_path / "net.lc0ex.json").read_text())
+    assert restored["metadata"] == "ZmluZ2VycHJpbnQ=" and restored["target"] == ["NVIDIA", "sm_100a"]
+    assert restored["magic"] == 0x1C0E and restored["format"] == 1
+    with pytest.raises(ValueError):
+        B.ExecutableBuilder().build_and_write(tmp_path / "incomplete.lc0ex.json")
+
+
+# ------------------------------------------------------------------ calls and dependencies
+
+def test_call_serializes_kernel_metadata_and_argument_offsets() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    kernel = builder.add_kernel(_artifact(parameters=(POINTER, POINTER, POINTER)))
+    program.call(kernel, _external(builder, "first"), _external(builder, "second"), _external(builder, "third"))
+    executable = builder.build()
+    node = executable.programs[0].nodes[0]
+    assert executable.kernels[0].function == "kernel" and node.grid == (2, 3, 1) and node.block == (128, 1, 1)
+    assert node.dynamic_shared_memory_bytes == 256
+    assert [(a.kind, a.offset) for a in node.arguments] == [("persistent", 0), ("persistent", 2), ("persistent", 4)]
+
+
+def test_null_pointer_slots_belong_to_the_runtime_and_the_count_is_checked() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    kernel = builder.add_kernel(_artifact(parameters=(POINTER, NULL_POINTER, POINTER)))
+    first, second = _external(builder, "first"), _external(builder, "second")
+    program.call(kernel, first, second)
+    executable = builder.build()
+    assert list(executable.kernels[0].parameters) == [POINTER, NULL_POINTER, POINTER]
+    assert [a.offset for a in executable.programs[0].nodes[0].arguments] == [0, 2]
+    with pytest.raises(ValueError, match="Kernel call has 3 arguments; expected 2."):
+        program.call(kernel, first, second, first)
+
+
+def test_readonly_weights_order_nothing_and_writers_order_readers_and_writers() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    kernel = builder.add_kernel(_artifact())
+    weights = _external(builder, "weights")
+    program.call(kernel, weights)
+    program.call(kernel, weights)
+    output = _external(builder, "output", writable=True)
+    program.call(kernel, output)                       # 2: write
+    program.call(kernel, output, readonly=(output,))   # 3: read  -> after 2
+    program.call(kernel, output)                       # 4: write -> after 3 (and 2, implied)
+    nodes = builder.build().programs[0].nodes
+    assert [n.dependencies for n in nodes] == [[], [], [], [2], [3]]
+
+
+def test_dependencies_are_transitively_reduced_but_keep_independent_readers() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    one = builder.add_kernel(_artifact())
+    two = builder.add_kernel(_artifact(function="two", parameters=(POINTER, POINTER)))
+    x, y = _external(builder, "x", writable=True), _external(builder, "y", writable=True)
+    program.call(one, x)                          # 0: write x
+    program.call(two, x, y, readonly=(x,))        # 1: read x, write y   -> [0]
+    program.call(two, x, y, readonly=(x, y))      # 2: read x, read y    -> [1]      (0 is implied by 1)
+    program.call(one, x, readonly=(x,))           # 3: read x            -> [0]
+    program.call(one, x)                          # 4: write x           -> [2, 3]   (readers 1, 2, 3; 1 implied by 2)
+    nodes = builder.build().programs[0].nodes
+    assert [n.dependencies for n in nodes] == [[], [0], [1], [0], [2, 3]]
+
+
+def test_ordered_temporaries_share_one_range_and_prefer_a_slot_of_their_own_size() -> None:
+    builder = _builder()
+    program = builder.program(name="main")
+    kernel = builder.add_kernel(_artifact(parameters=(POINTER, POINTER)))
+    first = program.temporary_buffer(size_bytes=64, alignment_bytes=32)
+    second = program.temporary_buffer(size_bytes=64, alignment_bytes=32)
+    bridge = _external(builder, "bridge", writable=True)
+    program.call(kernel, first, bridge)
+    program.call(kernel, bridge, second, readonly=(bridge,))
+    main = builder.build().programs[0]
+    assert main.execution_allocation.size_bytes == 64
+    assert main.nodes[0].arguments[0].offset == main.nodes[1].arguments[1].offset
+    assert main.nodes[1].dependencies == [0]
+    # a chain 256 -> 64 -> 256 -> 64 bytes: each range is dead two steps later, and a slot of the same size is preferred
+    builder = _builder()
+    program = builder.program(name="chain")
+    kernel = builder.add_kernel(_artifact(parameters=(POINTER, POINTER)))
+    sizes = [256, 64, 256, 64]
+    temps = [program.temporary_buffer(size_bytes=s, alignment_bytes=64) for s in sizes]
+    for src, dst in zip(temps, temps[1:]):
+        program.call(kernel, dst, src, readonly=(src,))
+    chain = builder.build().programs[0]
+    offsets = {}
+    for node, (src, dst) in zip(chain.nodes, zip(range(3), range(1, 4))):
+        offsets[dst], offsets[src] = node.arguments[0].offset, node.arguments[1].offset
+    assert offsets[2] == offsets[0] and offsets[3] == offsets[1] and offsets[0] != offsets[1]
+    assert chain.execution_allocation.size_bytes == 256 + 64
+
+
+def test_equal_artifacts_are_one_kernel_and_symbols_are_pointer_arguments() -> None:
+    builder = _builder()
+    assert builder.add_kernel(_artifact()) is builder.add_kernel(_artifact())
+    program = builder.program(name="main")
+    kernel = builder.add_kernel(_artifact(parameters=(POINTER, POINTER)))
+    output = _external(builder, "output", writable=True)
+    symbol = builder.add_symbol(B.SymbolArtifact(B.BinaryFormat.CUBIN, b"fake cubin", "mapping_table"))
+    program.call(kernel, output, symbol)
+    executable = builder.build()
+    argument = executable.programs[0].nodes[0].arguments[1]
+    assert isinstance(symbol, B.SymbolHandle) and len(executable.binaries) == 1
+    assert (argument.kind, argument.binary_idx, argument.symbol_name, argument.offset) == ("symbol", 0, "mapping_table", None)
+
+
+# ------------------------------------------------------------------ kernel artifacts of this library
+
+def test_compiled_artifacts_are_pointer_only_with_static_launch_metadata() -> None:
+    ln = B.compile_kernel("layer_norm_skip", {"ROWS": 640, "WIDTH": 1024, "ACTIVATION": 0, "EPSILON": "1e-3f"})
+    assert ln.binary_data[:4] == b"\x7fELF" and ln.function.encode() in ln.binary_data
+    assert ln.parameters == (POINTER,) * 7 and ln.grid == (80, 1, 1) and ln.block == (256, 1, 1)
+    assert ln.dynamic_shared_memory_bytes == 0
+    assert set(B.adapters()) >= {"layer_norm", "layer_norm_skip", "softmax_64"}
+    with pytest.raises(ValueError):
+        B.compile_kernel("softmax_64", {})
+    # and it links: weights persistent, activations temporaries, one program
+    builder = _builder()
+    program = builder.program(name="batch-10")
+    kernel = builder.add_kernel(ln)
+    names = ("/encoder0/mha/out/dense/b/w", "/encoder0/ln1/w/scale", "/encoder0/ln1/w/bias")
+    bias, gamma, beta = (builder.persistent_buffer(name=n, shape=(1024,), dtype=BF16, alignment_bytes=16) for n in names)
+    alpha = builder.persistent_buffer(name="/encoder0/alpha*input/w", shape=(1,), dtype=BF16, alignment_bytes=16)
+    rows = [program.temporary_buffer(size_bytes=640 * 1024 * 2, alignment_bytes=256) for _ in range(3)]
+    program.call(kernel, rows[2], rows[0], bias, rows[1], gamma, beta, alpha, readonly=(rows[0], rows[1]))
+    executable = builder.build()
+    assert executable.programs[0].execution_allocation.size_bytes == 3 * 640 * 1024 * 2
+    assert len(executable.binaries) == 1 and executable.kernels[0].function == ln.function
+
+
+def _launch(artifact: B.KernelArtifact, pointers: list[int]) -> None:
+    """What an lc0ex runtime does with a node: load the binary, look the entry point up, launch it with its
+    static grid and block and the pointer arguments."""
+    import ctypes
+
+    from cuda.bindings import driver
+
+    def ok(result):
+        assert result[0] == driver.CUresult.CUDA_SUCCESS, result[0]
+        return result[1] if len(result) == 2 else result[1:]
+
+    module = ok(driver.cuModuleLoadData(artifact.binary_data))
+    function = ok(driver.cuModuleGetFunction(module, artifact.function.encode()))
+    values = (ctypes.c_void_p * len(pointers))(*pointers)
+    slots = (ctypes.c_void_p * len(pointers))(*[ctypes.addressof(values) + i * ctypes.sizeof(ctypes.c_void_p)
+                                                for i in range(len(pointers))])
+    stream = torch.cuda.current_stream().cuda_stream
+    result = driver.cuLaunchKernel(function, *artifact.grid, *artifact.block, artifact.dynamic_shared_memory_bytes,
+                                   stream, ctypes.addressof(slots), 0)
+    assert result[0] == driver.CUresult.CUDA_SUCCESS, result[0]
+    torch.cuda.synchronize()
+    ok(driver.cuModuleUnload(module))
+
+
+@pytest.mark.gpu
+def test_artifacts_run_as_an_lc0ex_runtime_would_launch_them() -> None:
+    torch.cuda.init()
+    torch.zeros(1, device="cuda")
+    gen = torch.Generator().manual_seed(11)
+    rows, width = 333, 1024
+    x, skip = (torch.randn((rows, width), generator=gen).to(torch.bfloat16) for _ in range(2))
+    bias, beta = (torch.randn(width, generator=gen).mul(0.3).to(torch.bfloat16) for _ in range(2))
+    gamma = (1 + 0.1 * torch.randn(width, generator=gen)).to(torch.bfloat16)
+    alpha = torch.tensor([0.43]).to(torch.bfloat16)
+    ln = B.compile_kernel("layer_norm_skip", {"ROWS": rows, "WIDTH": width, "ACTIVATION": 1, "EPSILON": "1e-3f"})
+    dev = [t.cuda() for t in (x, bias, skip, gamma, beta, alpha)]
+    out = torch.empty((rows, width), dtype=torch.bfloat16, device="cuda")
+    _launch(ln, [t.data_ptr() for t in (out, *dev)])
+    want = O.layer_norm(x.float(), bias.float(), gamma.float(), beta.float(), "mish", 1e-3, skip=skip.float(), alpha=alpha.float())
+    torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=8e-3)
+
+    rows = 5000
+    qk = (torch.randn((rows, 64), generator=gen) * 3).to(torch.bfloat16)
+    smolgen = (torch.randn((rows, 64), generator=gen) * 2).to(torch.bfloat16)
+    sm = B.compile_kernel("softmax_64", {"ROWS": rows})
+    probs = torch.empty((rows, 64), dtype=torch.bfloat16, device="cuda")
+    _launch(sm, [probs.data_ptr(), qk.cuda().data_ptr(), smolgen.cuda().data_ptr()])
+    torch.testing.assert_close(probs.float().cpu(), O.softmax_64(qk, smolgen).float(), rtol=8e-3, atol=2e-3)
