@@ -285,7 +285,7 @@ LC0B200_API int lc0b200_layer_norm(void* out, const void* in, const void* bias, 
   if (has_skip) { REQUIRE_PTR(skip); REQUIRE_PTR(alpha); }
   if ((q_out == nullptr) != (q_scale == nullptr)) return LC0B200_ERR_NULL_POINTER;
   if (out == nullptr && q_out == nullptr) return LC0B200_ERR_NULL_POINTER;  // out may be NULL only with q_out
-  REQUIRE_SHAPE(row_count >= 0 && width > 0 && epsilon >= 0.0f);
+  REQUIRE_SHAPE(row_count >= 0 && row_count <= 0x7FFFFFFFLL && width > 0 && epsilon >= 0.0f);
   if (activation != LC0B200_ACT_NONE && activation != LC0B200_ACT_MISH && activation != LC0B200_ACT_SWISH) {
     return LC0B200_ERR_UNSUPPORTED;
   }
@@ -329,7 +329,7 @@ LC0B200_API int lc0b200_normalize_quantize_rows(void* out, float* scale, const v
                                                 const void* gamma, const void* beta, long long row_count, int width,
                                                 float epsilon, void* stream) {
   REQUIRE_PTR(out); REQUIRE_PTR(scale); REQUIRE_PTR(z); REQUIRE_PTR(stats); REQUIRE_PTR(gamma); REQUIRE_PTR(beta);
-  REQUIRE_SHAPE(row_count >= 0 && width > 0 && parts > 0 && epsilon > 0.0f && row_count <= 8LL * 0x7FFFFFFF);
+  REQUIRE_SHAPE(row_count >= 0 && width > 0 && parts > 0 && epsilon > 0.0f && row_count <= 0x7FFFFFFFLL);
   return normalize_quantize_rows(out, scale, z, stats, parts, gamma, beta, row_count, width, epsilon, S(stream));
 }
 

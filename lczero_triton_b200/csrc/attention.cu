@@ -299,7 +299,7 @@ __device__ __forceinline__ void load_qk_chunk(uint8_t* stage, const QkParams& p,
   }
 }
 
-__global__ void __launch_bounds__(128) qk_mma_kernel(const QkParams p) {
+__device__ __forceinline__ void qk_mma_body(const QkParams p) {
   __shared__ __align__(16) uint8_t smem[2 * 2 * kTileBytes];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3, mi = lane >> 3, ri = lane & 7;
@@ -338,6 +338,9 @@ __global__ void __launch_bounds__(128) qk_mma_kernel(const QkParams p) {
     *reinterpret_cast<uint32_t*>(out + (16 * warp + g) * 64 + col) = pack_bf16x2(s[j][0] * scale, s[j][1] * scale);
     *reinterpret_cast<uint32_t*>(out + (16 * warp + g + 8) * 64 + col) = pack_bf16x2(s[j][2] * scale, s[j][3] * scale);
   }
+}
+__global__ void __launch_bounds__(128) qk_mma_kernel(const QkParams p) {
+  qk_mma_body(p);
 }
 
 // Generic CUDA-core forms of the three batched products (any m, n, k): one thread per output.

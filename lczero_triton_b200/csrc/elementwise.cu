@@ -21,7 +21,7 @@ inline unsigned grid_for(long long elements, int per_block = kBlock) {
 }
 
 // expand_planes.py:26-42
-__global__ void expand_planes_kernel(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
+__device__ __forceinline__ void expand_planes_body(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
                                      const float* __restrict__ values, long long plane_count) {
   const long long total = plane_count * 64;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -32,9 +32,13 @@ __global__ void expand_planes_kernel(bf16* __restrict__ out, const uint64_t* __r
     out[i] = ((masks[plane] >> sq) & 1ull) ? v : __float2bfloat16_rn(0.0f);
   }
 }
+__global__ void expand_planes_kernel(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
+                                     const float* __restrict__ values, long long plane_count) {
+  expand_planes_body(out, masks, values, plane_count);
+}
 
 // nchw_to_nhwc.py:26-44
-__global__ void nchw_to_nhwc_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, long long total,
+__device__ __forceinline__ void nchw_to_nhwc_body(bf16* __restrict__ out, const bf16* __restrict__ in, long long total,
                                     int input_channels, int output_channels, int hw) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -45,9 +49,13 @@ __global__ void nchw_to_nhwc_kernel(bf16* __restrict__ out, const bf16* __restri
     out[i] = in[(b * input_channels + c) * hw + s];
   }
 }
+__global__ void nchw_to_nhwc_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, long long total,
+                                    int input_channels, int output_channels, int hw) {
+  nchw_to_nhwc_body(out, in, total, input_channels, output_channels, hw);
+}
 
 // preprocess_attention_body.py:26-61
-__global__ void preprocess_attention_body_kernel(bf16* __restrict__ out, const bf16* __restrict__ planes,
+__device__ __forceinline__ void preprocess_attention_body_body(bf16* __restrict__ out, const bf16* __restrict__ planes,
                                                  const bf16* __restrict__ encoding, long long total,
                                                  int input_channels, int encoding_channels) {
   const int width = input_channels + encoding_channels;
@@ -61,9 +69,14 @@ __global__ void preprocess_attention_body_kernel(bf16* __restrict__ out, const b
                                 : encoding[token * encoding_channels + (c - input_channels)];
   }
 }
+__global__ void preprocess_attention_body_kernel(bf16* __restrict__ out, const bf16* __restrict__ planes,
+                                                 const bf16* __restrict__ encoding, long long total,
+                                                 int input_channels, int encoding_channels) {
+  preprocess_attention_body_body(out, planes, encoding, total, input_channels, encoding_channels);
+}
 
 // input_gating.py:26-51
-__global__ void input_gating_kernel(bf16* out, const bf16* in, const bf16* __restrict__ mult,
+__device__ __forceinline__ void input_gating_body(bf16* out, const bf16* in, const bf16* __restrict__ mult,
                                     const bf16* __restrict__ add, long long total, long long gate_elements) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -71,6 +84,10 @@ __global__ void input_gating_kernel(bf16* out, const bf16* in, const bf16* __res
     const float x = __bfloat162float(in[i]);
     out[i] = __float2bfloat16_rn(x * __bfloat162float(mult[g]) + __bfloat162float(add[g]));
   }
+}
+__global__ void input_gating_kernel(bf16* out, const bf16* in, const bf16* __restrict__ mult,
+                                    const bf16* __restrict__ add, long long total, long long gate_elements) {
+  input_gating_body(out, in, mult, add, total, gate_elements);
 }
 
 // Same, eight channels per thread with 16-byte accesses (gate_elements a multiple of 8).
@@ -93,7 +110,7 @@ __global__ void input_gating_vec_kernel(uint4* out, const uint4* in, const uint4
 
 // add_vectors.py:37-66 (period = bias_element_count, rows = 1) and
 // add_bias_batched.py:35-66 (bias row chosen by i / (row_count * channel_count)).
-__global__ void add_bias_kernel(bf16* out, const bf16* in, const bf16* __restrict__ bias, long long total,
+__device__ __forceinline__ void add_bias_body(bf16* out, const bf16* in, const bf16* __restrict__ bias, long long total,
                                 int channels, long long elements_per_batch, int activation) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -102,6 +119,10 @@ __global__ void add_bias_kernel(bf16* out, const bf16* in, const bf16* __restric
     const float x = __bfloat162float(in[i]) + __bfloat162float(bias[bt * channels + c]);
     out[i] = __float2bfloat16_rn(activate_rt(x, activation));
   }
+}
+__global__ void add_bias_kernel(bf16* out, const bf16* in, const bf16* __restrict__ bias, long long total,
+                                int channels, long long elements_per_batch, int activation) {
+  add_bias_body(out, in, bias, total, channels, elements_per_batch, activation);
 }
 
 // fused_qkv.py:132-183: three independent row-broadcast bias adds in one launch.
@@ -112,7 +133,7 @@ struct QkvBiasParams {
   int width[3];
   long long rows;
 };
-__global__ void fused_qkv_bias_kernel(const QkvBiasParams p) {
+__device__ __forceinline__ void fused_qkv_bias_body(const QkvBiasParams p) {
   const int which = blockIdx.y;
   const long long total = p.rows * p.width[which];
   bf16* out = p.out[which];
@@ -124,17 +145,23 @@ __global__ void fused_qkv_bias_kernel(const QkvBiasParams p) {
     out[i] = __float2bfloat16_rn(__bfloat162float(in[i]) + __bfloat162float(bias[i % w]));
   }
 }
+__global__ void fused_qkv_bias_kernel(const QkvBiasParams p) {
+  fused_qkv_bias_body(p);
+}
 
 // copy_type_converted.py:26-34
-__global__ void widen_kernel(float* __restrict__ out, const bf16* __restrict__ in, long long total) {
+__device__ __forceinline__ void widen_body(float* __restrict__ out, const bf16* __restrict__ in, long long total) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     out[i] = __bfloat162float(in[i]);
   }
 }
+__global__ void widen_kernel(float* __restrict__ out, const bf16* __restrict__ in, long long total) {
+  widen_body(out, in, total);
+}
 
 // policy_map.py:28-49
-__global__ void policy_map_kernel(bf16* __restrict__ out, const bf16* __restrict__ in,
+__device__ __forceinline__ void policy_map_body(bf16* __restrict__ out, const bf16* __restrict__ in,
                                   const int32_t* __restrict__ table, long long total, int in_count, int out_count) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -143,6 +170,10 @@ __global__ void policy_map_kernel(bf16* __restrict__ out, const bf16* __restrict
     const int src = table[o];
     out[i] = (src >= 0 && src < in_count) ? in[b * in_count + src] : __float2bfloat16_rn(0.0f);
   }
+}
+__global__ void policy_map_kernel(bf16* __restrict__ out, const bf16* __restrict__ in,
+                                  const int32_t* __restrict__ table, long long total, int in_count, int out_count) {
+  policy_map_body(out, in, table, total, in_count, out_count);
 }
 
 // dst[c, r] = src[r, c] through a padded shared-memory tile.
@@ -244,6 +275,44 @@ __device__ __forceinline__ float amax8(const uint4& raw, float amax) {
   return amax;
 }
 
+// The common case - aligned rows of up to 2048 columns, a multiple of 8 - with the number of 16-byte groups a
+// lane keeps fixed at compile time, so that a 1024-wide row costs 4 registers of data per lane, not 8 (the
+// kernel is bound by how many rows the SM has in flight, i.e. by registers per thread).
+// Two rows (warps) per CTA: small CTAs keep more rows in flight and shorten the tail of the launch.
+constexpr int kQuantWarps = 2;
+
+template <int GROUPS>
+__global__ void __launch_bounds__(kQuantWarps * 32) quantize_rows_held_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
+                                                                     const bf16* __restrict__ in, long long rows,
+                                                                     int width, long long ld_in) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * static_cast<long long>(kQuantWarps) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const uint4* src = reinterpret_cast<const uint4*>(in + row * ld_in);
+  uint2* dst = reinterpret_cast<uint2*>(out + row * width);
+  const int groups = width >> 3;
+  uint4 keep[GROUPS];
+#pragma unroll
+  for (int i = 0; i < GROUPS; ++i) {
+    const int g = lane + 32 * i;
+    keep[i] = g < groups ? __ldg(src + g) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < GROUPS; ++i) amax = amax8(keep[i], amax);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 1.0f;
+  if (lane == 0) scale[row] = s;
+#pragma unroll
+  for (int i = 0; i < GROUPS; ++i) {
+    const int g = lane + 32 * i;
+    if (g < groups) dst[g] = quantize8(keep[i], inv);
+  }
+}
+
+// Any width, pitch and alignment.
 __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
                                                                 const bf16* __restrict__ in, long long rows,
                                                                 int width, long long ld_in) {
@@ -402,10 +471,23 @@ int embed_concat(void* out, const uint64_t* masks, const float* values, const vo
 
 int quantize_rows(void* out, float* scale, const void* in, long long rows, int width, long long ld_in,
                   cudaStream_t st) {
-  const long long blocks = ceil_div_ll(rows, kBlock / 32);
-  quantize_rows_kernel<<<static_cast<unsigned>(blocks), kBlock, 0, st>>>(reinterpret_cast<int8_t*>(out), scale,
-                                                                       reinterpret_cast<const bf16*>(in), rows, width,
-                                                                       ld_in);
+  const unsigned blocks = static_cast<unsigned>(ceil_div_ll(rows, kBlock / 32));
+  const unsigned held_blocks = static_cast<unsigned>(ceil_div_ll(rows, kQuantWarps));
+  constexpr int kHeldThreads = kQuantWarps * 32;
+  auto* q = reinterpret_cast<int8_t*>(out);
+  const auto* x = reinterpret_cast<const bf16*>(in);
+  const bool held = (width % 8) == 0 && (ld_in % 8) == 0 && width <= 2048 && aligned16(in) && aligned16(out) &&
+                    rows <= 0x7FFFFFFFLL;
+  if (held) {
+    const int g = (width + 255) / 256;
+    if (g <= 1) quantize_rows_held_kernel<1><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+    else if (g <= 2) quantize_rows_held_kernel<2><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+    else if (g <= 4) quantize_rows_held_kernel<4><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+    else if (g <= 6) quantize_rows_held_kernel<6><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+    else quantize_rows_held_kernel<8><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+  } else {
+    quantize_rows_kernel<<<blocks, kBlock, 0, st>>>(q, scale, x, rows, width, ld_in);
+  }
   return launch_status();
 }
 

@@ -15,7 +15,7 @@ namespace lc0b200 {
 
 namespace {
 
-constexpr int kWarpsPerBlock = 8;
+constexpr int kWarpsPerBlock = 2;  // measured: 2 beats 4 and 8 by 2-7 % on every row kernel here (more CTAs in flight, shorter tail)
 constexpr int kMaxGroups = 8;  // 16-byte groups of 8 channels per lane: 32 lanes x 8 x 8 = 2048 channels
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -54,18 +54,38 @@ struct LnParams {
   float epsilon;
 };
 
-// One warp per row; GROUPS = ceil(width / 256) register groups per lane.  The body is a device function
-// so that a pointer-only entry point with baked shapes can wrap it too (lc0ex_bridge.py).
-template <int GROUPS>
+// One warp per row; GROUPS = ceil(width / 256) register groups per lane.  ACT / SKIP / QUANT fix the
+// activation, the presence of the skip operand and of the int8 output at compile time (-1 = decided at run
+// time from the parameters): the kernel is a stream of 16-byte loads and a few dozen instructions per
+// element, and with everything decided per element at run time it issued instructions for 54 % of its
+// cycles and reached two thirds of the memory bandwidth.  The combinations the forward pass uses are
+// instantiated; anything else takes the run-time form.  All loads of a row are issued before any
+// arithmetic.  The body is a device function so that a pointer-only entry point with baked shapes can
+// wrap it too (lc0ex_bridge.py).
+template <int GROUPS, int ACT, int SKIP, int QUANT>
 __device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kWarpsPerBlock) + (threadIdx.x >> 5);
   if (row >= p.rows) return;
+  const bool has_skip = SKIP < 0 ? p.has_skip != 0 : SKIP != 0;
+  const bool quant = QUANT < 0 ? p.q_out != nullptr : QUANT != 0;
   const int groups = p.width >> 3;
   const uint4* in = reinterpret_cast<const uint4*>(p.in + row * p.width);
-  const uint4* skip = p.has_skip ? reinterpret_cast<const uint4*>(p.skip + row * p.width) : nullptr;
+  const uint4* skip = reinterpret_cast<const uint4*>(p.skip + row * p.width);
   const uint4* bias = reinterpret_cast<const uint4*>(p.bias);
-  const float alpha = p.has_skip ? __bfloat162float(*p.alpha) : 1.0f;
+
+  uint4 raw_in[GROUPS], raw_skip[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int idx = lane + 32 * g;
+    raw_in[g] = make_uint4(0u, 0u, 0u, 0u);
+    raw_skip[g] = make_uint4(0u, 0u, 0u, 0u);
+    if (idx < groups) {
+      raw_in[g] = in[idx];
+      if (has_skip) raw_skip[g] = skip[idx];
+    }
+  }
+  const float alpha = has_skip ? __bfloat162float(*p.alpha) : 1.0f;
 
   float v[GROUPS][8];
   float sum = 0.0f;
@@ -73,15 +93,15 @@ __device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
   for (int g = 0; g < GROUPS; ++g) {
     const int idx = lane + 32 * g;
     if (idx < groups) {
-      float x[8], b[8];
-      unpack8(in[idx], x);
+      float x[8], b[8], s[8];
+      unpack8(raw_in[g], x);
       unpack8(__ldg(bias + idx), b);
-      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (p.has_skip) unpack8(skip[idx], s);
+      unpack8(raw_skip[g], s);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = activate_rt(x[j] + b[j], p.activation);
-        if (p.has_skip) t = alpha * t + s[j];
+        float t = x[j] + b[j];
+        t = ACT < 0 ? activate_rt(t, p.activation) : activate<(ACT < 0 ? 0 : ACT)>(t);
+        if (has_skip) t = alpha * t + s[j];
         v[g][j] = t;
         sum += t;
       }
@@ -124,16 +144,18 @@ __device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
         const float y0 = v[g][2 * j] * rstd * ga[2 * j] + be[2 * j];
         const float y1 = v[g][2 * j + 1] * rstd * ga[2 * j + 1] + be[2 * j + 1];
         w[j] = pack_bf16x2(y0, y1);
-        // Keep the bf16-rounded result: the quantiser below must see what is stored.
-        const float2 r = unpack_bf16x2(w[j]);
-        v[g][2 * j] = r.x;
-        v[g][2 * j + 1] = r.y;
-        amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
+        if (quant) {
+          // Keep the bf16-rounded result: the quantiser below must see what is stored.
+          const float2 r = unpack_bf16x2(w[j]);
+          v[g][2 * j] = r.x;
+          v[g][2 * j + 1] = r.y;
+          amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
+        }
       }
       if (p.out != nullptr) out[idx] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
-  if (p.q_out != nullptr) {
+  if (quant) {
     amax = warp_max(amax);
     const float s = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 1.0f;
@@ -150,9 +172,9 @@ __device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
   }
 }
 
-template <int GROUPS>
+template <int GROUPS, int ACT, int SKIP, int QUANT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(const LnParams p) {
-  layer_norm_warp_body<GROUPS>(p);
+  layer_norm_warp_body<GROUPS, ACT, SKIP, QUANT>(p);
 }
 
 // One CTA per row, row cached in shared memory as fp32 (any width, any alignment).
@@ -202,32 +224,45 @@ __global__ void __launch_bounds__(256) layer_norm_block_kernel(const LnParams p)
 }
 
 // Wide rows (the 8192-wide smolgen LayerNorm): one CTA of 256 threads per row, the row held in
-// registers as GROUPS 16-byte groups per thread, two block reductions through shared memory.
-template <int GROUPS>
+// registers as GROUPS 16-byte groups per thread, two block reductions through shared memory.  ACT / SKIP as in
+// the one-warp kernel: fixed at compile time for what the forward pass runs (swish, no skip), -1 = run time.
+template <int GROUPS, int ACT, int SKIP>
 __global__ void __launch_bounds__(256) layer_norm_wide_kernel(const LnParams p) {
   __shared__ float red[2][8];
   const long long row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups = p.width >> 3;
+  const bool has_skip = SKIP < 0 ? p.has_skip != 0 : SKIP != 0;
   const uint4* in = reinterpret_cast<const uint4*>(p.in + row * p.width);
-  const uint4* skip = p.has_skip ? reinterpret_cast<const uint4*>(p.skip + row * p.width) : nullptr;
+  const uint4* skip = reinterpret_cast<const uint4*>(p.skip + row * p.width);
   const uint4* bias = reinterpret_cast<const uint4*>(p.bias);
-  const float alpha = p.has_skip ? __bfloat162float(*p.alpha) : 1.0f;
+  uint4 raw_in[GROUPS], raw_skip[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {  // every load of the row before any arithmetic
+    const int idx = threadIdx.x + 256 * g;
+    raw_in[g] = make_uint4(0u, 0u, 0u, 0u);
+    raw_skip[g] = make_uint4(0u, 0u, 0u, 0u);
+    if (idx < groups) {
+      raw_in[g] = in[idx];
+      if (has_skip) raw_skip[g] = skip[idx];
+    }
+  }
+  const float alpha = has_skip ? __bfloat162float(*p.alpha) : 1.0f;
   float v[GROUPS][8];
   float sum = 0.0f;
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g) {
     const int idx = threadIdx.x + 256 * g;
     if (idx < groups) {
-      float x[8], b[8];
-      unpack8(in[idx], x);
+      float x[8], b[8], s[8];
+      unpack8(raw_in[g], x);
       unpack8(__ldg(bias + idx), b);
-      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (p.has_skip) unpack8(skip[idx], s);
+      unpack8(raw_skip[g], s);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = activate_rt(x[j] + b[j], p.activation);
-        if (p.has_skip) t = alpha * t + s[j];
+        float t = x[j] + b[j];
+        t = ACT < 0 ? activate_rt(t, p.activation) : activate<(ACT < 0 ? 0 : ACT)>(t);
+        if (has_skip) t = alpha * t + s[j];
         v[g][j] = t;
         sum += t;
       }
@@ -286,8 +321,23 @@ __global__ void __launch_bounds__(256) layer_norm_wide_kernel(const LnParams p) 
 
 template <int GROUPS>
 int launch_warp(const LnParams& p, cudaStream_t st) {
-  const long long blocks = ceil_div_ll(p.rows, kWarpsPerBlock);
-  layer_norm_warp_kernel<GROUPS><<<static_cast<unsigned>(blocks), kWarpsPerBlock * 32, 0, st>>>(p);
+  const unsigned blocks = static_cast<unsigned>(ceil_div_ll(p.rows, kWarpsPerBlock));
+  constexpr int kThreads = kWarpsPerBlock * 32;
+  const bool quant = p.q_out != nullptr;
+  // The combinations the forward pass runs, decided at compile time; the rest at run time.
+  if (p.activation == LC0B200_ACT_NONE && p.has_skip && !quant) {
+    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 0><<<blocks, kThreads, 0, st>>>(p);
+  } else if (p.activation == LC0B200_ACT_NONE && p.has_skip && quant) {
+    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 1><<<blocks, kThreads, 0, st>>>(p);
+  } else if (p.activation == LC0B200_ACT_NONE && !p.has_skip && !quant) {
+    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+  } else if (p.activation == LC0B200_ACT_MISH && !p.has_skip && !quant) {
+    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_MISH, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+  } else if (p.activation == LC0B200_ACT_SWISH && !p.has_skip && !quant) {
+    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_SWISH, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+  } else {
+    layer_norm_warp_kernel<GROUPS, -1, -1, -1><<<blocks, kThreads, 0, st>>>(p);
+  }
   return launch_status();
 }
 
@@ -425,12 +475,16 @@ int layer_norm(void* out, const void* in, const void* bias, const void* skip, co
   if (wide_vec) {
     const int g = (width / 8 + 255) / 256;
     const unsigned grid = static_cast<unsigned>(rows);
+    const bool swish_plain = activation == LC0B200_ACT_SWISH && !has_skip;  // the smolgen LayerNorms
     if (g <= 2) {
-      layer_norm_wide_kernel<2><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) layer_norm_wide_kernel<2, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
+      else layer_norm_wide_kernel<2, -1, -1><<<grid, 256, 0, st>>>(p);
     } else if (g <= 4) {
-      layer_norm_wide_kernel<4><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) layer_norm_wide_kernel<4, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
+      else layer_norm_wide_kernel<4, -1, -1><<<grid, 256, 0, st>>>(p);
     } else {
-      layer_norm_wide_kernel<8><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) layer_norm_wide_kernel<8, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
+      else layer_norm_wide_kernel<8, -1, -1><<<grid, 256, 0, st>>>(p);
     }
     return launch_status();
   }

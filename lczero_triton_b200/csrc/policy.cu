@@ -34,7 +34,7 @@ __device__ __forceinline__ void promotion_offsets(float (&dst)[3], const bf16* k
 }
 
 // One CTA (8 warps) per position.
-__global__ void __launch_bounds__(256) promotion_logits_kernel(bf16* records, const bf16* __restrict__ keys,
+__device__ __forceinline__ void promotion_logits_body(bf16* records, const bf16* __restrict__ keys,
                                                                const bf16* __restrict__ w, int width) {
   __shared__ float offs[8][3];
   const long long b = blockIdx.x;
@@ -49,6 +49,10 @@ __global__ void __launch_bounds__(256) promotion_logits_kernel(bf16* records, co
     const float qk = __bfloat162float(rec[(48 + s) * 64 + 56 + t]);
     rec[kPromoStart + threadIdx.x] = __float2bfloat16_rn(qk + offs[t][c]);
   }
+}
+__global__ void __launch_bounds__(256) promotion_logits_kernel(bf16* records, const bf16* __restrict__ keys,
+                                                               const bf16* __restrict__ w, int width) {
+  promotion_logits_body(records, keys, w, width);
 }
 
 __global__ void __launch_bounds__(256) policy_tail_kernel(float* __restrict__ out, const bf16* __restrict__ records,

@@ -545,35 +545,95 @@ class Adapter:
     launch: object
 
 
+_LN_WARPS_PER_BLOCK = 2  # kWarpsPerBlock of csrc/layernorm.cu: one warp per row, this many rows per CTA
+
+
 def _ln_launch(c: dict) -> tuple[tuple[int, int, int], tuple[int, int, int], int]:
-    return ((-(-c["ROWS"] // 8), 1, 1), (256, 1, 1), 0)
+    return ((-(-c["ROWS"] // _LN_WARPS_PER_BLOCK), 1, 1), (32 * _LN_WARPS_PER_BLOCK, 1, 1), 0)
 
 
+def _stream_launch(total_of):
+    """Grid of the grid-stride element-wise kernels: one thread per element up to 32 CTAs per SM of a B200."""
+    def launch(c: dict) -> tuple[tuple[int, int, int], tuple[int, int, int], int]:
+        return ((max(1, min(-(-total_of(c) // 256), 148 * 32)), 1, 1), (256, 1, 1), 0)
+    return launch
+
+
+_BF, _CBF = "bf16*", "const bf16*"
+
+# Entry-point parameters follow the reference's kernel ABI: outputs, then inputs, then weights; the integers
+# each reference specialization bakes in are the constants here.  (K/ = bt4/kernels/ of the reference.)
 _ADAPTERS: dict[str, Adapter] = {
     # K/layer_norm.py:37-161, the variant with a skip operand; ABI order of T/test_layer_norm.py:412-415.
     "layer_norm_skip": Adapter(
         "layernorm.cu",
-        (("bf16*", "out"), ("const bf16*", "in"), ("const bf16*", "bias"), ("const bf16*", "skip"),
-         ("const bf16*", "gamma"), ("const bf16*", "beta"), ("const bf16*", "alpha")),
+        ((_BF, "out"), (_CBF, "in"), (_CBF, "bias"), (_CBF, "skip"), (_CBF, "gamma"), (_CBF, "beta"), (_CBF, "alpha")),
         ("ROWS", "WIDTH", "ACTIVATION", "EPSILON"),
         "LnParams p = {out, in, bias, skip, gamma, beta, alpha, nullptr, nullptr, ROWS, WIDTH, ACTIVATION, 1, EPSILON};\n"
-        "  layer_norm_warp_body<(WIDTH + 255) / 256>(p);",
+        "  layer_norm_warp_body<(WIDTH + 255) / 256, ACTIVATION, 1, 0>(p);",
         _ln_launch),
     "layer_norm": Adapter(
         "layernorm.cu",
-        (("bf16*", "out"), ("const bf16*", "in"), ("const bf16*", "bias"), ("const bf16*", "gamma"),
-         ("const bf16*", "beta")),
+        ((_BF, "out"), (_CBF, "in"), (_CBF, "bias"), (_CBF, "gamma"), (_CBF, "beta")),
         ("ROWS", "WIDTH", "ACTIVATION", "EPSILON"),
         "LnParams p = {out, in, bias, nullptr, gamma, beta, nullptr, nullptr, nullptr, ROWS, WIDTH, ACTIVATION, 0, EPSILON};\n"
-        "  layer_norm_warp_body<(WIDTH + 255) / 256>(p);",
+        "  layer_norm_warp_body<(WIDTH + 255) / 256, ACTIVATION, 0, 0>(p);",
         _ln_launch),
     # K/softmax_64.py:45-71
     "softmax_64": Adapter(
-        "attention.cu",
-        (("bf16*", "out"), ("const bf16*", "scaled_qk"), ("const bf16*", "smolgen")),
-        ("ROWS",),
+        "attention.cu", ((_BF, "out"), (_CBF, "scaled_qk"), (_CBF, "smolgen")), ("ROWS",),
         "softmax_64_body(out, scaled_qk, smolgen, ROWS);",
         lambda c: ((-(-c["ROWS"] // 8), 1, 1), (256, 1, 1), 0)),
+    # K/batched_matmul.py:68-141, 64 x 64 outputs: body_qk (INTERLEAVED 1, OUT_STRIDE 4096) and policy_qk (0, 4288)
+    "qk_64": Adapter(
+        "attention.cu", ((_BF, "out"), (_CBF, "q"), (_CBF, "k"), (_CBF, "scale")),
+        ("BATCH_COUNT", "DEPTH", "HEADS", "INTERLEAVED", "OUT_STRIDE"),
+        "QkParams p = {out, q, k, scale, OUT_STRIDE, DEPTH, HEADS, INTERLEAVED};\n  qk_mma_body(p);",
+        lambda c: ((c["BATCH_COUNT"], 1, 1), (128, 1, 1), 0)),
+    # K/expand_planes.py:26-42
+    "expand_planes": Adapter(
+        "elementwise.cu", ((_BF, "out"), ("const uint64_t*", "masks"), ("const float*", "values")), ("PLANE_COUNT",),
+        "expand_planes_body(out, masks, values, PLANE_COUNT);", _stream_launch(lambda c: c["PLANE_COUNT"] * 64)),
+    # K/nchw_to_nhwc.py:26-44
+    "nchw_to_nhwc": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "in")), ("BATCH", "INPUT_CHANNELS", "OUTPUT_CHANNELS", "HW"),
+        "nchw_to_nhwc_body(out, in, (long long)BATCH * HW * OUTPUT_CHANNELS, INPUT_CHANNELS, OUTPUT_CHANNELS, HW);",
+        _stream_launch(lambda c: c["BATCH"] * c["HW"] * c["OUTPUT_CHANNELS"])),
+    # K/preprocess_attention_body.py:26-61
+    "preprocess_attention_body": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "planes"), (_CBF, "encoding")),
+        ("BATCH", "INPUT_CHANNELS", "ENCODING_CHANNELS"),
+        "preprocess_attention_body_body(out, planes, encoding, (long long)BATCH * 64 * (INPUT_CHANNELS + ENCODING_CHANNELS),"
+        " INPUT_CHANNELS, ENCODING_CHANNELS);",
+        _stream_launch(lambda c: c["BATCH"] * 64 * (c["INPUT_CHANNELS"] + c["ENCODING_CHANNELS"]))),
+    # K/input_gating.py:26-51
+    "input_gating": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "in"), (_CBF, "mult"), (_CBF, "add")), ("BATCH", "SQUARES", "CHANNELS"),
+        "input_gating_body(out, in, mult, add, (long long)BATCH * SQUARES * CHANNELS, (long long)SQUARES * CHANNELS);",
+        _stream_launch(lambda c: c["BATCH"] * c["SQUARES"] * c["CHANNELS"])),
+    # K/add_vectors.py:37-66: out[i] = act(in[i] + bias[i mod BIAS_ELEMENTS])
+    "add_vectors": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "in"), (_CBF, "bias")), ("ELEMENTS", "BIAS_ELEMENTS", "ACTIVATION"),
+        "add_bias_body(out, in, bias, ELEMENTS, BIAS_ELEMENTS, ELEMENTS, ACTIVATION);",
+        _stream_launch(lambda c: c["ELEMENTS"])),
+    # K/add_bias_batched.py:35-66: out[bt,row,c] = act(in[bt,row,c] + bias[bt,c])
+    "add_bias_batched": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "in"), (_CBF, "bias")), ("BATCH_COUNT", "ROWS", "CHANNELS", "ACTIVATION"),
+        "add_bias_body(out, in, bias, (long long)BATCH_COUNT * ROWS * CHANNELS, CHANNELS, (long long)ROWS * CHANNELS, ACTIVATION);",
+        _stream_launch(lambda c: c["BATCH_COUNT"] * c["ROWS"] * c["CHANNELS"])),
+    # K/copy_type_converted.py:26-34
+    "copy_type_converted": Adapter(
+        "elementwise.cu", (("float*", "out"), (_CBF, "in")), ("ELEMENTS",),
+        "widen_body(out, in, ELEMENTS);", _stream_launch(lambda c: c["ELEMENTS"])),
+    # K/policy_map.py:28-49 (the table is the module symbol the reference exports, K/mapping_table.py:68-89: a pointer)
+    "policy_map": Adapter(
+        "elementwise.cu", ((_BF, "out"), (_CBF, "in"), ("const int32_t*", "table")), ("BATCH", "IN_COUNT", "OUT_COUNT"),
+        "policy_map_body(out, in, table, (long long)BATCH * OUT_COUNT, IN_COUNT, OUT_COUNT);",
+        _stream_launch(lambda c: c["BATCH"] * c["OUT_COUNT"])),
+    # K/promotion_logits.py:67-145 (ABI order records, keys, weights)
+    "promotion_logits": Adapter(
+        "policy.cu", ((_BF, "records"), (_CBF, "keys"), (_CBF, "w")), ("BATCH", "WIDTH"),
+        "promotion_logits_body(records, keys, w, WIDTH);", lambda c: ((c["BATCH"], 1, 1), (256, 1, 1), 0)),
 }
 
 

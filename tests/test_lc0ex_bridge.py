@@ -210,9 +210,11 @@ def test_equal_artifacts_are_one_kernel_and_symbols_are_pointer_arguments() -> N
 def test_compiled_artifacts_are_pointer_only_with_static_launch_metadata() -> None:
     ln = B.compile_kernel("layer_norm_skip", {"ROWS": 640, "WIDTH": 1024, "ACTIVATION": 0, "EPSILON": "1e-3f"})
     assert ln.binary_data[:4] == b"\x7fELF" and ln.function.encode() in ln.binary_data
-    assert ln.parameters == (POINTER,) * 7 and ln.grid == (80, 1, 1) and ln.block == (256, 1, 1)
+    assert ln.parameters == (POINTER,) * 7 and ln.grid == (320, 1, 1) and ln.block == (64, 1, 1)
     assert ln.dynamic_shared_memory_bytes == 0
-    assert set(B.adapters()) >= {"layer_norm", "layer_norm_skip", "softmax_64"}
+    assert set(B.adapters()) >= {"layer_norm", "layer_norm_skip", "softmax_64", "qk_64", "expand_planes", "nchw_to_nhwc",
+                                 "preprocess_attention_body", "input_gating", "add_vectors", "add_bias_batched",
+                                 "copy_type_converted", "policy_map", "promotion_logits"}
     with pytest.raises(ValueError):
         B.compile_kernel("softmax_64", {})
     # and it links: weights persistent, activations temporaries, one program
@@ -229,10 +231,14 @@ def test_compiled_artifacts_are_pointer_only_with_static_launch_metadata() -> No
     assert len(executable.binaries) == 1 and executable.kernels[0].function == ln.function
 
 
-def _launch(artifact: B.KernelArtifact, pointers: list[int]) -> None:
+def _launch(artifact: B.KernelArtifact, tensors: list[torch.Tensor]) -> None:
     """What an lc0ex runtime does with a node: load the binary, look the entry point up, launch it with its
-    static grid and block and the pointer arguments."""
+    static grid and block and the pointer arguments.  (``tensors`` are device tensors; holding them here keeps
+    their memory from being handed out again before the kernel has run.)"""
     import ctypes
+
+    assert all(t.is_cuda for t in tensors)
+    pointers = [t.data_ptr() for t in tensors]
 
     from cuda.bindings import driver
 
@@ -266,7 +272,7 @@ def test_artifacts_run_as_an_lc0ex_runtime_would_launch_them() -> None:
     ln = B.compile_kernel("layer_norm_skip", {"ROWS": rows, "WIDTH": width, "ACTIVATION": 1, "EPSILON": "1e-3f"})
     dev = [t.cuda() for t in (x, bias, skip, gamma, beta, alpha)]
     out = torch.empty((rows, width), dtype=torch.bfloat16, device="cuda")
-    _launch(ln, [t.data_ptr() for t in (out, *dev)])
+    _launch(ln, [out, *dev])
     want = O.layer_norm(x.float(), bias.float(), gamma.float(), beta.float(), "mish", 1e-3, skip=skip.float(), alpha=alpha.float())
     torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=8e-3)
 
@@ -275,5 +281,52 @@ def test_artifacts_run_as_an_lc0ex_runtime_would_launch_them() -> None:
     smolgen = (torch.randn((rows, 64), generator=gen) * 2).to(torch.bfloat16)
     sm = B.compile_kernel("softmax_64", {"ROWS": rows})
     probs = torch.empty((rows, 64), dtype=torch.bfloat16, device="cuda")
-    _launch(sm, [probs.data_ptr(), qk.cuda().data_ptr(), smolgen.cuda().data_ptr()])
+    _launch(sm, [probs, qk.cuda(), smolgen.cuda()])
     torch.testing.assert_close(probs.float().cpu(), O.softmax_64(qk, smolgen).float(), rtol=8e-3, atol=2e-3)
+
+
+@pytest.mark.gpu
+def test_element_wise_and_gather_artifacts_match_the_oracle() -> None:
+    from lczero_triton_b200 import mapping_table
+    from lczero_triton_b200.synthetic import synthetic_planes
+
+    torch.zeros(1, device="cuda")
+    gen = torch.Generator().manual_seed(12)
+    bf = torch.bfloat16
+    batch = 5
+    # expand_planes (exact)
+    masks, values = synthetic_planes(batch, 3)
+    planes = torch.empty((batch, 112, 64), dtype=bf, device="cuda")
+    _launch(B.compile_kernel("expand_planes", {"PLANE_COUNT": batch * 112}),
+            [planes, masks.cuda(), values.cuda()])
+    assert torch.equal(planes.float().cpu(), O.expand_planes(masks, values, bf).float())
+    # add_vectors with mish, input_gating
+    x = torch.randn((batch * 64, 128), generator=gen).to(bf)
+    bias = torch.randn(128, generator=gen).to(bf)
+    out = torch.empty_like(x, device="cuda")
+    _launch(B.compile_kernel("add_vectors", {"ELEMENTS": x.numel(), "BIAS_ELEMENTS": 128, "ACTIVATION": 1}),
+            [out, x.cuda(), bias.cuda()])
+    torch.testing.assert_close(out.float().cpu(), O.add_vectors(x.float(), bias.float(), "mish"), rtol=8e-3, atol=4e-3)
+    mult, add = (torch.randn((64, 128), generator=gen).to(bf) for _ in range(2))
+    _launch(B.compile_kernel("input_gating", {"BATCH": batch, "SQUARES": 64, "CHANNELS": 128}),
+            [out, x.cuda(), mult.cuda(), add.cuda()])
+    want = O.input_gating(x.float().reshape(batch, 64, 128), mult.float(), add.float()).reshape(-1, 128)
+    torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=4e-3)
+    # body_qk on the tensor cores, policy_map and the f32 widening (exact)
+    heads = 4
+    q, k = (torch.randn((batch, 64, heads * 32), generator=gen).mul(0.5).to(bf) for _ in range(2))
+    scale = torch.tensor([0.173]).to(bf)
+    scores = torch.empty((batch, heads, 64, 64), dtype=bf, device="cuda")
+    _launch(B.compile_kernel("qk_64", {"BATCH_COUNT": batch * heads, "DEPTH": 32, "HEADS": heads, "INTERLEAVED": 1,
+                                       "OUT_STRIDE": 4096}),
+            [scores, q.cuda(), k.cuda(), scale.cuda()])
+    torch.testing.assert_close(scores.float().cpu(), O.body_qk(q, k, float(scale.float()), heads), rtol=1e-2, atol=1e-2)
+    records = torch.randn((batch, 4288), generator=gen).to(bf)
+    table = torch.tensor(mapping_table.values(), dtype=torch.int32)
+    gathered = torch.empty((batch, 1858), dtype=bf, device="cuda")
+    _launch(B.compile_kernel("policy_map", {"BATCH": batch, "IN_COUNT": 4288, "OUT_COUNT": 1858}),
+            [gathered, records.cuda(), table.cuda()])
+    assert torch.equal(gathered.float().cpu(), O.policy_map(records, table).float())
+    wide = torch.empty((batch, 1858), dtype=torch.float32, device="cuda")
+    _launch(B.compile_kernel("copy_type_converted", {"ELEMENTS": batch * 1858}), [wide, gathered])
+    assert torch.equal(wide.cpu(), gathered.float().cpu())
