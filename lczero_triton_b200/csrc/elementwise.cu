@@ -1,6 +1,9 @@
 // Layout, element-wise and quantisation kernels (all HBM-bound; one pass, 64-bit indexing).
 // Each kernel names the reference Triton kernel it replaces; paths are relative to
 // packages/lczero-triton/src/lczero_triton/bt4/kernels/.
+// Kernels with a reference counterpart are written as a __device__ body plus a thin __global__ entry:
+// lc0ex_bridge.py wraps the same body in an extern "C" entry point whose parameters are pointers only and
+// whose shapes are compile-time constants (the contract of an lc0ex kernel artifact).
 #include <cuda_runtime.h>
 
 #include "common.cuh"
@@ -22,7 +25,7 @@ inline unsigned grid_for(long long elements, int per_block = kBlock) {
 
 // expand_planes.py:26-42
 __device__ __forceinline__ void expand_planes_body(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
-                                     const float* __restrict__ values, long long plane_count) {
+                                                   const float* __restrict__ values, long long plane_count) {
   const long long total = plane_count * 64;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -39,7 +42,7 @@ __global__ void expand_planes_kernel(bf16* __restrict__ out, const uint64_t* __r
 
 // nchw_to_nhwc.py:26-44
 __device__ __forceinline__ void nchw_to_nhwc_body(bf16* __restrict__ out, const bf16* __restrict__ in, long long total,
-                                    int input_channels, int output_channels, int hw) {
+                                                  int input_channels, int output_channels, int hw) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int c = static_cast<int>(i % output_channels);
@@ -56,8 +59,8 @@ __global__ void nchw_to_nhwc_kernel(bf16* __restrict__ out, const bf16* __restri
 
 // preprocess_attention_body.py:26-61
 __device__ __forceinline__ void preprocess_attention_body_body(bf16* __restrict__ out, const bf16* __restrict__ planes,
-                                                 const bf16* __restrict__ encoding, long long total,
-                                                 int input_channels, int encoding_channels) {
+                                                               const bf16* __restrict__ encoding, long long total,
+                                                               int input_channels, int encoding_channels) {
   const int width = input_channels + encoding_channels;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -77,7 +80,7 @@ __global__ void preprocess_attention_body_kernel(bf16* __restrict__ out, const b
 
 // input_gating.py:26-51
 __device__ __forceinline__ void input_gating_body(bf16* out, const bf16* in, const bf16* __restrict__ mult,
-                                    const bf16* __restrict__ add, long long total, long long gate_elements) {
+                                                  const bf16* __restrict__ add, long long total, long long gate_elements) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long g = i % gate_elements;
@@ -111,7 +114,7 @@ __global__ void input_gating_vec_kernel(uint4* out, const uint4* in, const uint4
 // add_vectors.py:37-66 (period = bias_element_count, rows = 1) and
 // add_bias_batched.py:35-66 (bias row chosen by i / (row_count * channel_count)).
 __device__ __forceinline__ void add_bias_body(bf16* out, const bf16* in, const bf16* __restrict__ bias, long long total,
-                                int channels, long long elements_per_batch, int activation) {
+                                              int channels, long long elements_per_batch, int activation) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long bt = i / elements_per_batch;
@@ -162,7 +165,7 @@ __global__ void widen_kernel(float* __restrict__ out, const bf16* __restrict__ i
 
 // policy_map.py:28-49
 __device__ __forceinline__ void policy_map_body(bf16* __restrict__ out, const bf16* __restrict__ in,
-                                  const int32_t* __restrict__ table, long long total, int in_count, int out_count) {
+                                                const int32_t* __restrict__ table, long long total, int in_count, int out_count) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int o = static_cast<int>(i % out_count);
@@ -212,9 +215,9 @@ __global__ void embed_position_input_kernel(bf16* __restrict__ out, const uint64
 // (expand_planes.py + preprocess_attention_body.py; network.py:458-465,521-533).
 // One CTA per position; each thread moves 16-byte groups of 8 channels.
 __global__ void __launch_bounds__(kBlock) embed_concat_kernel(bf16* __restrict__ out,
-                                                               const uint64_t* __restrict__ masks,
-                                                               const float* __restrict__ values,
-                                                               const bf16* __restrict__ position, int enc) {
+                                                              const uint64_t* __restrict__ masks,
+                                                              const float* __restrict__ values,
+                                                              const bf16* __restrict__ position, int enc) {
   __shared__ uint64_t s_mask[112];
   __shared__ uint16_t s_val[112];
   const long long b = blockIdx.x;
@@ -283,8 +286,8 @@ constexpr int kQuantWarps = 2;
 
 template <int GROUPS>
 __global__ void __launch_bounds__(kQuantWarps * 32) quantize_rows_held_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
-                                                                     const bf16* __restrict__ in, long long rows,
-                                                                     int width, long long ld_in) {
+                                                                              const bf16* __restrict__ in, long long rows,
+                                                                              int width, long long ld_in) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kQuantWarps) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -314,8 +317,8 @@ __global__ void __launch_bounds__(kQuantWarps * 32) quantize_rows_held_kernel(in
 
 // Any width, pitch and alignment.
 __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
-                                                                const bf16* __restrict__ in, long long rows,
-                                                                int width, long long ld_in) {
+                                                               const bf16* __restrict__ in, long long rows,
+                                                               int width, long long ld_in) {
   constexpr int kHeld = 8;  // 16-byte groups a lane keeps in registers: 8 * 32 lanes * 8 values = 2048 columns
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kBlock / 32) + (threadIdx.x >> 5);

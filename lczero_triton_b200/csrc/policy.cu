@@ -35,7 +35,7 @@ __device__ __forceinline__ void promotion_offsets(float (&dst)[3], const bf16* k
 
 // One CTA (8 warps) per position.
 __device__ __forceinline__ void promotion_logits_body(bf16* records, const bf16* __restrict__ keys,
-                                                               const bf16* __restrict__ w, int width) {
+                                                      const bf16* __restrict__ w, int width) {
   __shared__ float offs[8][3];
   const long long b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -330,3 +330,91 @@ def test_element_wise_and_gather_artifacts_match_the_oracle() -> None:
     wide = torch.empty((batch, 1858), dtype=torch.float32, device="cuda")
     _launch(B.compile_kernel("copy_type_converted", {"ELEMENTS": batch * 1858}), [wide, gathered])
     assert torch.equal(wide.cpu(), gathered.float().cpu())
+
+
+def _execute(executable: B.Executable, program_index: int, persistent: dict[str, torch.Tensor],
+             inputs: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """A minimal lc0ex runtime for the tests: one allocation for the persistent buffers, one for the program,
+    named buffers filled by name, nodes launched in an order that respects their dependency lists (here: index
+    order, checked), every argument resolved to allocation base + offset.  Returns the program's named buffers."""
+    program = executable.programs[program_index]
+    element = {B.DataType.F32: torch.float32, B.DataType.BF16: torch.bfloat16, B.DataType.F16: torch.float16,
+               B.DataType.U8: torch.uint8, B.DataType.U64: torch.int64}
+    arenas = {"persistent": torch.zeros(executable.persistent_allocation.size_bytes + 256, dtype=torch.uint8, device="cuda"),
+              "execution": torch.zeros(program.execution_allocation.size_bytes + 256, dtype=torch.uint8, device="cuda")}
+
+    def view(kind: str, buffer: B.NamedBuffer) -> torch.Tensor:
+        count = 1
+        for extent in buffer.shape:
+            count *= extent
+        nbytes = count * B.data_type_size_bytes(buffer.data_type)
+        return arenas[kind][buffer.offset:buffer.offset + nbytes].view(element[buffer.data_type]).reshape(buffer.shape)
+
+    for buffer in executable.buffers:
+        view("persistent", buffer).copy_(persistent[buffer.name])
+    named = {buffer.name: view("execution", buffer) for buffer in program.buffers}
+    for name, value in inputs.items():
+        named[name].copy_(value)
+    done: set[int] = set()
+    for index, node in enumerate(program.nodes):
+        assert all(dep in done for dep in node.dependencies), (index, node.dependencies)
+        kernel = executable.kernels[node.kernel_idx]
+        artifact = B.KernelArtifact(*executable.binaries[kernel.binary_idx], kernel.function, kernel.parameters,
+                                    node.grid, node.block, node.dynamic_shared_memory_bytes)
+        pointers = [arenas[a.kind][a.offset:] for a in node.arguments]
+        _launch(artifact, pointers)
+        done.add(index)
+    return named
+
+
+@pytest.mark.gpu
+def test_a_linked_program_runs_the_policy_tail_of_the_graph() -> None:
+    """network.py:1261-1356 as an lc0ex program of pointer-only kernels: policy QK into the 4288-slot record,
+    promotion logits in place, gather through the table, widening to f32.  Weights and the table are named
+    persistent buffers, Q / K the program's named inputs, the record and the gathered logits temporaries that
+    the linker places, the f32 logits the named output; the run is checked against the oracle's policy head."""
+    from lczero_triton_b200 import mapping_table
+
+    torch.zeros(1, device="cuda")
+    gen = torch.Generator().manual_seed(21)
+    batch, width = 6, 128
+    bf = torch.bfloat16
+    q, k = (torch.randn((batch, 64, width), generator=gen).mul(0.4).to(bf) for _ in range(2))
+    promotion_w = torch.randn((width, 4), generator=gen).mul(0.3).to(bf)
+    scale = torch.tensor([width ** -0.5]).to(bf)
+    table = torch.tensor(mapping_table.values(), dtype=torch.int32)
+
+    builder = B.ExecutableBuilder().set_target(B.Vendor.NVIDIA, "sm_100a")
+    program = builder.program(name=f"batch-{batch}")
+    qk = builder.add_kernel(B.compile_kernel("qk_64", {"BATCH_COUNT": batch, "DEPTH": width, "HEADS": 1, "INTERLEAVED": 0,
+                                                       "OUT_STRIDE": 4288}))
+    promo = builder.add_kernel(B.compile_kernel("promotion_logits", {"BATCH": batch, "WIDTH": width}))
+    gather = builder.add_kernel(B.compile_kernel("policy_map", {"BATCH": batch, "IN_COUNT": 4288, "OUT_COUNT": 1858}))
+    widen = builder.add_kernel(B.compile_kernel("copy_type_converted", {"ELEMENTS": batch * 1858}))
+    w_scale = builder.persistent_buffer(name="/policy/scale/w", shape=(1,), dtype=BF16, alignment_bytes=256)
+    w_promo = builder.persistent_buffer(name="/policy/promotion/matmul/w", shape=(width, 4), dtype=BF16, alignment_bytes=256)
+    # the reference exports the table as a module symbol; a named persistent buffer of raw bytes serves here
+    w_table = builder.persistent_buffer(name="/policy/mapping_table", shape=(1858 * 4,), dtype=U8, alignment_bytes=256)
+    in_q = program.buffer(name="/policy/Q", shape=(batch, 64, width), dtype=BF16, alignment_bytes=256)
+    in_k = program.buffer(name="/policy/K", shape=(batch, 64, width), dtype=BF16, alignment_bytes=256)
+    out = program.buffer(name="/output/policy", shape=(batch, 1858), dtype=F32, writable=True, alignment_bytes=256)
+    records = program.temporary_buffer(size_bytes=batch * 4288 * 2, alignment_bytes=256)
+    gathered = program.temporary_buffer(size_bytes=batch * 1858 * 2, alignment_bytes=256)
+    program.call(qk, records, in_q, in_k, w_scale)
+    program.call(promo, records, in_k, w_promo)
+    program.call(gather, gathered, records, w_table, readonly=(records,))
+    program.call(widen, out, gathered, readonly=(gathered,))
+    executable = builder.build()
+    nodes = executable.programs[0].nodes
+    assert [n.dependencies for n in nodes] == [[], [0], [1], [2]]
+    assert executable.programs[0].execution_allocation.size_bytes >= batch * (2 * 64 * width * 2 + 1858 * 4 + 4288 * 2)
+
+    named = _execute(executable, 0,
+                     {"/policy/scale/w": scale.cuda(), "/policy/promotion/matmul/w": promotion_w.cuda(),
+                      "/policy/mapping_table": table.cuda().view(torch.uint8)},
+                     {"/policy/Q": q.cuda(), "/policy/K": k.cuda()})
+    want_records = O.policy_qk(q, k, float(scale.float()))
+    want_records = want_records.to(bf).float()
+    want_records[:, 4096:] = O.promotion_logits(want_records, k, promotion_w).to(bf).float()
+    want = O.policy_map(want_records, table).float()
+    torch.testing.assert_close(named["/output/policy"].cpu(), want, rtol=1.6e-2, atol=1.6e-2)
