@@ -127,7 +127,13 @@ LC0B200_API int lc0b200_batched_matmul(void* out_bf16, const void* a_bf16, const
  *       = acc * row_scale[m] * col_scale[n]   (int8 inputs; both scales f32, may be NULL = 1)
  *   out = act(y + bias[n])     (bias bf16, may be NULL), stored as bf16 / f32,
  *   or the raw s32 accumulator when out_kind == LC0B200_OUT_S32 (no scale, bias or activation).
- * lda / ldw / ldc are row pitches in elements. */
+ * lda / ldw / ldc are row pitches in elements.
+ * Two projections of the same A as one product: with out_tail_bf16 set, output columns [0, n_main) go to
+ * `out` (pitch ldc >= n_main) and columns [n_main, n) to out_tail_bf16 (pitch ldc_tail >= n - n_main); W, bias
+ * and the ln_in vectors cover all n columns.  bf16 output only, n_main a multiple of 256, not with the residual
+ * epilogue; the tensor-core kernel only (operands it cannot take are refused, not sent to the CUDA-core one).
+ * A ragged last tile costs tensor-core time for its own width (rounded up to 32), not for a whole tile, so a
+ * 32-wide projection rides on a 3072-wide one for about one per cent of its time. */
 typedef struct lc0b200_gemm_args {
   void* out;
   const void* a;
@@ -171,6 +177,10 @@ typedef struct lc0b200_gemm_args {
   int res_parts;
   float res_alpha;
   float* stats_out;
+  /* ---- second output for the trailing columns (all zero = off) */
+  void* out_tail_bf16;
+  long long ldc_tail;
+  int n_main;
 } lc0b200_gemm_args;
 LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* args_host, void* stream);
 /* Same contract on the plain CUDA-core kernel (any shape / alignment; used for the tiny head
@@ -294,7 +304,7 @@ LC0B200_API int lc0b200_output_probabilities(float* policy_probs, float* wdl_pro
  * weights as uploaded, the operands derived from them and the workspace for max_batch positions.
  * create / destroy allocate and free only a small host structure.  set_weight copies host memory to the
  * arena on `stream`; finalize derives the GEMM operands (transposes, LayerNorm folding) and synchronises
- * `stream` once; forward only launches (about 185 kernels at 15 layers) and neither allocates nor
+ * `stream` once; forward only launches (about 170 kernels at 15 layers) and neither allocates nor
  * synchronises, so it can be captured into a CUDA graph.  One forward at a time per network object. */
 typedef struct lc0b200_net lc0b200_net;
 typedef struct lc0b200_net_config {

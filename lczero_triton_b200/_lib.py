@@ -36,6 +36,7 @@ class GemmArgs(ctypes.Structure):
         ("res_skip_bf16", c_void_p), ("ld_skip", c_longlong), ("res_stats", c_void_p),
         ("res_gamma_bf16", c_void_p), ("res_beta_bf16", c_void_p), ("res_parts", c_int), ("res_alpha", c_float),
         ("stats_out", c_void_p),
+        ("out_tail_bf16", c_void_p), ("ldc_tail", c_longlong), ("n_main", c_int),
     ]
 
 

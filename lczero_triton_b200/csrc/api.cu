@@ -184,7 +184,12 @@ static int check_gemm(const lc0b200_gemm_args* g) {
   REQUIRE_PTR(g);
   REQUIRE_PTR(g->out); REQUIRE_PTR(g->a); REQUIRE_PTR(g->w);
   REQUIRE_SHAPE(g->m >= 0 && g->n > 0 && g->k > 0);
-  REQUIRE_SHAPE(g->lda >= g->k && g->ldc >= g->n);
+  const bool has_tail = g->out_tail_bf16 != nullptr;
+  if (has_tail) {
+    REQUIRE_SHAPE(g->n_main > 0 && g->n_main < g->n && g->n_main % 256 == 0 && g->ldc_tail >= g->n - g->n_main);
+    if (g->out_kind != LC0B200_OUT_BF16 || g->res_skip_bf16 != nullptr || g->stats_out != nullptr) return LC0B200_ERR_UNSUPPORTED;
+  }
+  REQUIRE_SHAPE(g->lda >= g->k && g->ldc >= (has_tail ? g->n_main : g->n));
   REQUIRE_SHAPE(g->ldw >= (g->w_layout == LC0B200_W_KN ? g->n : g->k));
   if (g->in_type != LC0B200_IN_BF16 && g->in_type != LC0B200_IN_INT8) return LC0B200_ERR_UNSUPPORTED;
   if (g->out_kind < LC0B200_OUT_BF16 || g->out_kind > LC0B200_OUT_S32) return LC0B200_ERR_UNSUPPORTED;
@@ -212,7 +217,7 @@ LC0B200_API int lc0b200_gemm(const lc0b200_gemm_args* g, void* stream) {
   if (st != LC0B200_OK) return st;
   if (g->m == 0) return LC0B200_OK;
   if (gemm_tcgen05_supported(*g)) return gemm_tcgen05(*g, S(stream));
-  if (has_deferred_layer_norm(g)) return LC0B200_ERR_UNSUPPORTED;
+  if (has_deferred_layer_norm(g) || g->out_tail_bf16 != nullptr) return LC0B200_ERR_UNSUPPORTED;
   return gemm_simt(*g, S(stream));
 }
 
@@ -220,7 +225,7 @@ LC0B200_API int lc0b200_gemm_simt(const lc0b200_gemm_args* g, void* stream) {
   const int st = check_gemm(g);
   if (st != LC0B200_OK) return st;
   if (g->m == 0) return LC0B200_OK;
-  if (has_deferred_layer_norm(g)) return LC0B200_ERR_UNSUPPORTED;
+  if (has_deferred_layer_norm(g) || g->out_tail_bf16 != nullptr) return LC0B200_ERR_UNSUPPORTED;
   return gemm_simt(*g, S(stream));
 }
 

@@ -83,6 +83,12 @@ struct TileCfg {
 
 struct KernelParams {
   void* out;
+  // Columns [n_main, n) of the product go to a second bf16 matrix (a projection that shares A with the main
+  // one: smolgen's compression rides on the QKV GEMM).  n_main is a multiple of 256, so a tile is wholly main
+  // or wholly tail; n_main == n when there is no tail.
+  bf16* out_tail;
+  long long ldc_tail;
+  int n_main;
   const bf16* bias;
   const float* row_scale;
   const float* col_scale;
@@ -429,11 +435,22 @@ __device__ __forceinline__ float acc_value(uint32_t raw, float rs, const float* 
   return __uint_as_float(raw);
 }
 
+// Width (N) of the MMAs of the n-tile that starts at column `tile_n0`: the whole tile width, or, for a bf16
+// product with K-major weights whose last tile is ragged, the columns that exist rounded up to 32 - the
+// tensor core then spends time on 32 columns instead of 256 for a 32-wide tail.  (32 is a valid N for both
+// the single-CTA M = 128 and the CTA-pair M = 256 shapes; a pair splits it 16 + 16 between its CTAs.)
+template <int BN, bool INT8, bool W_KN>
+__device__ __forceinline__ int mma_width(int n, int tile_n0) {
+  if (INT8 || W_KN || BN < 32) return BN;
+  const int left = n - tile_n0;
+  return left >= BN ? BN : ((left + 31) & ~31);
+}
+
 template <int BN, bool INT8, bool W_KN, int CTAS, int MODE>
 __global__ void __launch_bounds__(TileCfg<BN, CTAS, MODE>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_skip,
-                    const KernelParams p) {
+                    const __grid_constant__ CUtensorMap map_tail, const KernelParams p) {
   using Cfg = TileCfg<BN, CTAS, MODE>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPerRow = INT8 ? 128 : 64;   // K elements per 128-byte row
@@ -497,6 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_w);
     if (p.tma_store) ptx::prefetch_tensormap(&map_out);
+    if (p.tma_store && p.n_main < p.n) ptx::prefetch_tensormap(&map_tail);
     if (MODE == kRes) ptx::prefetch_tensormap(&map_skip);
   }
   if (warp == 1) {
@@ -523,7 +541,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     for (long long tile = group; tile < num_tiles && ok; tile += num_groups) {
       const int m0 = static_cast<int>(tile / n_tiles) * kTileM + static_cast<int>(rank) * kBM;
-      const int n0 = static_cast<int>(tile % n_tiles) * BN + static_cast<int>(rank) * Cfg::kBRows;
+      // This CTA's share of the weight tile: rows [rank * width / CTAS, ...) of the tile, where width is what
+      // the MMAs of this tile cover (the box is always kBRows rows; rows past the share are not read).
+      const int tile_n0 = static_cast<int>(tile % n_tiles) * BN;
+      const int n0 = tile_n0 + static_cast<int>(rank) * (mma_width<BN, INT8, W_KN>(p.n, tile_n0) / CTAS);
       for (int kb = 0; kb < k_blocks; ++kb) {
         ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 0x100u + stage);
         ok = __all_sync(0xFFFFFFFFu, ok);
@@ -554,8 +575,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0) {
-      constexpr uint32_t idesc = ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kTileM),
-                                                 static_cast<uint32_t>(BN));
       int stage = 0;
       uint32_t phase = 0;
       uint32_t local = 0;
@@ -568,6 +587,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
+        const int tile_n0 = static_cast<int>(tile % n_tiles) * BN;
+        const uint32_t idesc = ptx::instr_desc(INT8 ? 2u : 1u, 1u, W_KN ? 1u : 0u, static_cast<uint32_t>(kTileM),
+                                               static_cast<uint32_t>(mma_width<BN, INT8, W_KN>(p.n, tile_n0)));
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 0x300u + stage);
           ok = __all_sync(0xFFFFFFFFu, ok);
@@ -781,8 +803,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
               for (int g = 0; g < Cfg::kGroups; ++g) {
                 if (n0 + g * 64 < p.n) {
-                  ptx::tma_store_2d(&map_out, staging + g * kGroupBytes, n0 + g * 64,
-                                    static_cast<int>(m0) + quarter * 32);
+                  const bool tail = n0 >= p.n_main;  // tiles never straddle n_main
+                  ptx::tma_store_2d(tail ? &map_tail : &map_out, staging + g * kGroupBytes,
+                                    n0 + g * 64 - (tail ? p.n_main : 0), static_cast<int>(m0) + quarter * 32);
                 }
               }
               ptx::bulk_commit();
@@ -803,7 +826,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t packed[16];
             float unused_sum = 0.0f, unused_sumsq = 0.0f;
             finish32<MODE, INT8, false>(v, packed, col0, nullptr, rc, p, unused_sum, unused_sumsq);
-            bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
+            bf16* dst = col0 >= p.n_main ? p.out_tail + row * p.ldc_tail + (col0 - p.n_main)
+                                         : reinterpret_cast<bf16*>(p.out) + row * p.ldc + col0;
             if (full_chunk) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
@@ -905,8 +929,16 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   const int out_eb = g.out_kind == LC0B200_OUT_BF16 ? 2 : 4;
   const bool tma_store = Cfg::kTmaStore && g.out_kind == LC0B200_OUT_BF16 && aligned16(g.out) &&
                          ((g.ldc * out_eb) % 16 == 0);
-  CUtensorMap map_out = map_a, map_skip = map_a;  // placeholders when unused
-  if (tma_store && !make_map(&map_out, g.out, 2, g.m, g.n, g.ldc, 32, 64)) return LC0B200_ERR_CUDA;
+  const bool has_tail = g.out_tail_bf16 != nullptr;
+  const int n_main = has_tail ? g.n_main : g.n;
+  if (has_tail && (MODE == kRes || n_main % BN != 0)) return LC0B200_ERR_UNSUPPORTED;
+  CUtensorMap map_out = map_a, map_skip = map_a, map_tail = map_a;  // placeholders when unused
+  if (tma_store && !make_map(&map_out, g.out, 2, g.m, n_main, g.ldc, 32, 64)) return LC0B200_ERR_CUDA;
+  if (has_tail && tma_store) {
+    // The tail shares the grouped epilogue with the main output, so it must be addressable the same way.
+    if (!aligned16(g.out_tail_bf16) || (g.ldc_tail % 8) != 0) return LC0B200_ERR_MISALIGNED;
+    if (!make_map(&map_tail, g.out_tail_bf16, 2, g.m, g.n - n_main, g.ldc_tail, 32, 64)) return LC0B200_ERR_CUDA;
+  }
   if (MODE == kRes) {
     if (!tma_store) return LC0B200_ERR_UNSUPPORTED;
     if (!aligned16(g.res_skip_bf16) || (g.ld_skip % 8) != 0) return LC0B200_ERR_MISALIGNED;
@@ -917,6 +949,9 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   if (allow_dynamic_smem(smem_opt_in, kernel, Cfg::kSmemBytes) != LC0B200_OK) return LC0B200_ERR_CUDA;
   KernelParams p;
   p.out = g.out;
+  p.out_tail = reinterpret_cast<bf16*>(g.out_tail_bf16);
+  p.ldc_tail = g.ldc_tail;
+  p.n_main = n_main;
   p.bias = reinterpret_cast<const bf16*>(g.bias_bf16);
   p.row_scale = g.row_scale;
   p.col_scale = g.col_scale;
@@ -928,7 +963,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   p.activation = g.activation;
   p.status = device_status_words();
   if (p.status == nullptr) return LC0B200_ERR_CUDA;
-  p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16)) &&
+  p.vec_ok = aligned16(g.out) && ((g.ldc * out_eb) % 16 == 0) && (!has_tail || (aligned16(g.out_tail_bf16) && g.ldc_tail % 8 == 0)) && (g.bias_bf16 == nullptr || aligned16(g.bias_bf16)) &&
              (g.col_scale == nullptr || aligned16(g.col_scale)) &&
              (g.ln_in_stats == nullptr || (aligned16(g.ln_in_c) && aligned16(g.ln_in_d))) &&
              (g.res_stats == nullptr || (aligned16(g.res_gamma_bf16) && aligned16(g.res_beta_bf16)));
@@ -963,7 +998,7 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = CTAS == 2 ? 1 : 0;
-  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, map_tail, p) != cudaSuccess) {
     (void)cudaGetLastError();  // reported here; do not leave it for an unrelated later call
     return LC0B200_ERR_CUDA;
   }

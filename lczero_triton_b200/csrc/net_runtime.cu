@@ -50,7 +50,10 @@ struct Dense {
 };
 
 struct Layer {
-  Dense compress_f, sg1, sg2, qkv_f, out, ffn1_f, ffn2;  // bf16 mode (LayerNorms folded into *_f)
+  // bf16 mode (LayerNorms folded into *_f).  When 3 * embedding is a multiple of 256, qkv_f also holds smolgen's
+  // compression as its trailing columns (one GEMM, second output: lc0b200_gemm_args::out_tail_bf16) and
+  // compress_f is unused.
+  Dense compress_f, sg1, sg2, qkv_f, out, ffn1_f, ffn2;
   Dense compress, qkv, ffn1;                             // int8 mode (stand-alone LayerNorms); out / ffn2 shared
   void* qkv_bias = nullptr;                              // int8 mode: Q, K, V biases back to back
 };
@@ -206,6 +209,10 @@ std::vector<std::pair<std::string, long long>> weight_table(const lc0b200_net_co
   return t;
 }
 
+// Q, K, V and smolgen's compression read the same rows; they run as one GEMM when its second output can
+// start at a multiple of 256 columns.
+bool fuse_compress(const lc0b200_net_config& c) { return !c.int8_gemms && (3 * c.embedding) % 256 == 0; }
+
 bool config_ok(const lc0b200_net_config& c) {
   return c.embedding > 0 && c.layers > 0 && c.heads > 0 && c.embedding % c.heads == 0 && c.embedding / c.heads == 32 &&
          c.ffn > 0 && c.pos_enc > 0 && c.smolgen_compress > 0 && c.smolgen_hidden > 0 && c.smolgen_gen > 0 &&
@@ -257,8 +264,12 @@ void plan(lc0b200_net& net) {
       quantised(l.ffn1, f, d);
       quantised(l.ffn2, d, f);
     } else {
-      folded(l.compress_f, c.smolgen_compress, d);
-      folded(l.qkv_f, 3 * d, d);
+      if (fuse_compress(c)) {
+        folded(l.qkv_f, 3 * d + c.smolgen_compress, d);
+      } else {
+        folded(l.compress_f, c.smolgen_compress, d);
+        folded(l.qkv_f, 3 * d, d);
+      }
       packed(l.out, d, d);
       folded(l.ffn1_f, f, d);
       packed(l.ffn2, d, f);
@@ -339,7 +350,7 @@ int run_gemm(void* out, const void* a, const Dense& w, long long m, int activati
 }
 
 int run_gemm_folded(const lc0b200_net& net, void* out, const void* z, const Dense& w, long long m, const float* stats,
-                    int activation, void* stream) {
+                    int activation, void* stream, void* out_tail = nullptr, int n_main = 0) {
   lc0b200_gemm_args g;
   std::memset(&g, 0, sizeof(g));
   g.out = out;
@@ -360,6 +371,12 @@ int run_gemm_folded(const lc0b200_net& net, void* out, const void* z, const Dens
   g.ln_in_d = w.fold_d;
   g.ln_in_parts = (w.k + 63) / 64;
   g.ln_eps = net.cfg.ln_eps;
+  if (out_tail != nullptr) {  // columns [n_main, n) to a matrix of their own
+    g.out_tail_bf16 = out_tail;
+    g.n_main = n_main;
+    g.ldc = n_main;
+    g.ldc_tail = w.n - n_main;
+  }
   return lc0b200_gemm(&g, stream);
 }
 
@@ -480,18 +497,23 @@ LC0B200_API int lc0b200_net_finalize(lc0b200_net* net, void* stream) {
     return lc0b200_transpose(const_cast<void*>(dense.w), dev(weight), dense.k, dense.n, 2, stream);
   };
   // Deferred LayerNorm: fold gamma / beta of `ln` into the (possibly concatenated) weight.
+  // The parts are laid side by side along N, each as wide as its weight says; an empty bias name is a part
+  // without bias.
   auto fold = [&](Dense& dense, const std::vector<std::string>& parts, const std::vector<std::string>& biases,
                   const std::string& ln) -> int {
-    const int each = dense.n / static_cast<int>(parts.size());
+    size_t off = 0;
     for (size_t i = 0; i < parts.size(); ++i) {
-      const size_t off = i * static_cast<size_t>(each);
-      fold_layer_norm_kernel<<<(each + 127) / 128, 128, 0, st>>>(
+      const int width = static_cast<int>(find(*net, parts[i])->count / dense.k);
+      const bool has_bias = !biases.empty() && !biases[i].empty();
+      fold_layer_norm_kernel<<<(width + 127) / 128, 128, 0, st>>>(
           reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dense.w)) + off * dense.k,
           const_cast<float*>(dense.fold_c) + off, const_cast<float*>(dense.fold_d) + off,
           static_cast<const __nv_bfloat16*>(dev(parts[i])), static_cast<const __nv_bfloat16*>(dev(ln + "/w/scale")),
           static_cast<const __nv_bfloat16*>(dev(ln + "/w/bias")),
-          biases.empty() ? nullptr : static_cast<const __nv_bfloat16*>(dev(biases[i])), dense.k, each);
+          has_bias ? static_cast<const __nv_bfloat16*>(dev(biases[i])) : nullptr, dense.k, width);
+      off += static_cast<size_t>(width);
     }
+    if (off != static_cast<size_t>(dense.n)) return LC0B200_ERR_BAD_SHAPE;
     return cudaGetLastError() == cudaSuccess ? LC0B200_OK : LC0B200_ERR_CUDA;
   };
   // int8 mode: `count` output channels of `weight` ([K, count] as uploaded) into rows [first, first + count)
@@ -530,9 +552,14 @@ LC0B200_API int lc0b200_net_finalize(lc0b200_net* net, void* stream) {
       l.ffn1.bias = dev(enc(i, "/ffn/dense1/b/w"));
       NET_TRY(quantise(l.ffn2, enc(i, "/ffn/dense2/w/w"), 0, l.ffn2.n));
     } else {
-      NET_TRY(fold(l.compress_f, {enc(i, "/smolgen/compress/w")}, {}, prev));
-      NET_TRY(fold(l.qkv_f, {enc(i, "/mha/Q/w/w"), enc(i, "/mha/K/w/w"), enc(i, "/mha/V/w/w")},
-                   {enc(i, "/mha/Q/b/w"), enc(i, "/mha/K/b/w"), enc(i, "/mha/V/b/w")}, prev));
+      if (fuse_compress(c)) {
+        NET_TRY(fold(l.qkv_f, {enc(i, "/mha/Q/w/w"), enc(i, "/mha/K/w/w"), enc(i, "/mha/V/w/w"), enc(i, "/smolgen/compress/w")},
+                     {enc(i, "/mha/Q/b/w"), enc(i, "/mha/K/b/w"), enc(i, "/mha/V/b/w"), ""}, prev));
+      } else {
+        NET_TRY(fold(l.compress_f, {enc(i, "/smolgen/compress/w")}, {}, prev));
+        NET_TRY(fold(l.qkv_f, {enc(i, "/mha/Q/w/w"), enc(i, "/mha/K/w/w"), enc(i, "/mha/V/w/w")},
+                     {enc(i, "/mha/Q/b/w"), enc(i, "/mha/K/b/w"), enc(i, "/mha/V/b/w")}, prev));
+      }
       NET_TRY(pack(l.out, enc(i, "/mha/out/dense/w/w"), nullptr));
       NET_TRY(fold(l.ffn1_f, {enc(i, "/ffn/dense1/w/w")}, {enc(i, "/ffn/dense1/b/w")}, enc(i, "/ln1")));
       NET_TRY(pack(l.ffn2, enc(i, "/ffn/dense2/w/w"), nullptr));
@@ -659,8 +686,12 @@ LC0B200_API int lc0b200_net_forward(lc0b200_net* net, const uint64_t* masks, con
   float* free_s[2] = {net->stats[1], net->stats[2]};
   for (int i = 0; i < c.layers; ++i) {
     const Layer& l = net->layers[i];
-    NET_TRY(run_gemm_folded(*net, net->qkv, z, l.qkv_f, t, stats, LC0B200_ACT_NONE, stream));
-    NET_TRY(run_gemm_folded(*net, net->compressed, z, l.compress_f, t, stats, LC0B200_ACT_NONE, stream));
+    if (fuse_compress(c)) {
+      NET_TRY(run_gemm_folded(*net, net->qkv, z, l.qkv_f, t, stats, LC0B200_ACT_NONE, stream, net->compressed, 3 * d));
+    } else {
+      NET_TRY(run_gemm_folded(*net, net->qkv, z, l.qkv_f, t, stats, LC0B200_ACT_NONE, stream));
+      NET_TRY(run_gemm_folded(*net, net->compressed, z, l.compress_f, t, stats, LC0B200_ACT_NONE, stream));
+    }
     // smolgen: per-position 64 x 64 logit bias for every head (network.py:778-849, 943-955)
     NET_TRY(run_gemm(net->sg_hidden, net->compressed, l.sg1, b, LC0B200_ACT_NONE, LC0B200_OUT_BF16, stream));
     NET_TRY(lc0b200_layer_norm(net->sg_hidden, net->sg_hidden, dev(enc(i, "/smolgen/dense1/b/w")), nullptr,

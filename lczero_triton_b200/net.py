@@ -113,16 +113,20 @@ class Bt4Net:
             return _Dense(packed, _lib.W_NK, n, k, bias)
         return _Dense(w_kn, _lib.W_KN, n, k, bias)
 
-    def _dense_folded(self, names: list[str], biases: list[str] | None, gamma: str, beta: str) -> _Dense:
+    def _dense_folded(self, names: list[str], biases: list[str | None] | None, gamma: str, beta: str) -> _Dense:
         """Dense layer(s) consuming a deferred-LayerNorm input: the weight is pre-scaled by the
-        LayerNorm's gamma and two per-column vectors carry the mean and beta terms."""
+        LayerNorm's gamma and two per-column vectors carry the mean and beta terms.  Several layers of the
+        same input are concatenated along N; a ``None`` among ``biases`` is a layer without bias."""
         w = torch.cat([self._w[n] for n in names], dim=1).float()  # [K, N], bf16 values
         g, b = self._w[gamma].float(), self._w[beta].float()
         scaled = (w * g[:, None]).to(torch.bfloat16)
         fold_c = scaled.float().sum(dim=0).contiguous()
         fold_d = b @ w
         if biases is not None:
-            fold_d = fold_d + torch.cat([self._w[x] for x in biases]).float()
+            parts = [self._w[x].float() if x is not None else
+                     torch.zeros(self._w[n].shape[1], dtype=torch.float32, device=self.device)
+                     for x, n in zip(biases, names)]
+            fold_d = fold_d + torch.cat(parts)
         k, n = scaled.shape
         if self._layout == _lib.W_NK:
             packed = torch.empty((n, k), dtype=torch.bfloat16, device=self.device)
@@ -151,17 +155,26 @@ class Bt4Net:
                 "ffn1": d(f"{p}/ffn/dense1/w/w", f"{p}/ffn/dense1/b/w", int8=q8),
                 "ffn2": d(f"{p}/ffn/dense2/w/w", int8=q8),
             })
+        # The second output of a GEMM starts at a multiple of 256 columns (lc0b200_gemm_args::n_main).
+        self._fuse_compress = self._layout == _lib.W_NK and (3 * self.cfg.embedding) % 256 == 0
         if self.deferred:
             self.zero_bias = torch.zeros(self.cfg.embedding, dtype=torch.bfloat16, device=self.device)
             for i, layer in enumerate(self.layers):
                 p = f"/encoder{i}"
                 prev = "/attn_body/ln2" if i == 0 else f"/encoder{i - 1}/ln2"
-                layer["compress_f"] = self._dense_folded([f"{p}/smolgen/compress/w"], None,
-                                                         f"{prev}/w/scale", f"{prev}/w/bias")
-                if not q8:  # the int8 GEMMs read a quantised LayerNorm output instead of folding it
-                    layer["qkv_f"] = self._dense_folded([f"{p}/mha/Q/w/w", f"{p}/mha/K/w/w", f"{p}/mha/V/w/w"],
-                                                        [f"{p}/mha/Q/b/w", f"{p}/mha/K/b/w", f"{p}/mha/V/b/w"],
+                qkv_w = [f"{p}/mha/Q/w/w", f"{p}/mha/K/w/w", f"{p}/mha/V/w/w"]
+                qkv_b = [f"{p}/mha/Q/b/w", f"{p}/mha/K/b/w", f"{p}/mha/V/b/w"]
+                if not q8 and self._fuse_compress:
+                    # Q, K, V and smolgen's compression all read the same rows: one GEMM, the compression as
+                    # its trailing columns, written to a buffer of its own (lc0b200_gemm_args::out_tail_bf16).
+                    layer["qkv_f"] = self._dense_folded([*qkv_w, f"{p}/smolgen/compress/w"], [*qkv_b, None],
                                                         f"{prev}/w/scale", f"{prev}/w/bias")
+                else:
+                    layer["compress_f"] = self._dense_folded([f"{p}/smolgen/compress/w"], None,
+                                                             f"{prev}/w/scale", f"{prev}/w/bias")
+                    if not q8:  # the int8 GEMMs read a quantised LayerNorm output instead of folding it
+                        layer["qkv_f"] = self._dense_folded(qkv_w, qkv_b, f"{prev}/w/scale", f"{prev}/w/bias")
+                if not q8:
                     layer["ffn1_f"] = self._dense_folded([f"{p}/ffn/dense1/w/w"], [f"{p}/ffn/dense1/b/w"],
                                                          f"{p}/ln1/w/scale", f"{p}/ln1/w/bias")
                 layer["out_b"] = self._w[f"{p}/mha/out/dense/b/w"]
@@ -340,9 +353,14 @@ class Bt4Net:
             if q8:
                 normalise_and_quantise(z, ln, stats)
                 self._gemm(ws["qkv"], qd, layer["qkv"], t, row_scale=qs)
+                self._gemm_folded(ws["compressed"], z, layer["compress_f"], t, stats)
+            elif self._fuse_compress:
+                f = layer["qkv_f"]
+                ops.gemm(ws["qkv"], z, f.w, m=t, n=f.n, k=f.k, w_layout=f.layout, ln_in=(stats, f.fold_c, f.fold_d),
+                         ln_eps=eps, out_tail=ws["compressed"], n_main=3 * d)
             else:
                 self._gemm_folded(ws["qkv"], z, layer["qkv_f"], t, stats)
-            self._gemm_folded(ws["compressed"], z, layer["compress_f"], t, stats)
+                self._gemm_folded(ws["compressed"], z, layer["compress_f"], t, stats)
             self._smolgen_and_attention(ws, layer, i, b)
             z1, stats1 = free_z[0], free_s[0]
             a_out, scale_out = ws["merged"], None

@@ -124,8 +124,12 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, *, m: int, n: int,
          ln_in: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None, ln_eps: float = 1e-3,
          res_skip: torch.Tensor | None = None, res_alpha: float = 1.0,
          res_ln: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
-         stats_out: torch.Tensor | None = None) -> torch.Tensor:
+         stats_out: torch.Tensor | None = None, out_tail: torch.Tensor | None = None,
+         n_main: int | None = None) -> torch.Tensor:
     """Tensor-core GEMM with fused epilogue (``include/lc0b200.h``: lc0b200_gemm).
+
+    ``out_tail`` / ``n_main``: two projections of the same ``a`` as one product - columns ``[0, n_main)`` of
+    the result go to ``out``, columns ``[n_main, n)`` to ``out_tail`` (bf16; ``n_main`` a multiple of 256).
 
     Deferred LayerNorm: ``ln_in=(stats [parts,m,2] f32, c [n] f32, d [n] f32)`` folds the LayerNorm of
     the rows of ``a`` into the epilogue; ``res_skip`` (+ ``res_ln=(stats, gamma, beta)`` when the skip
@@ -139,7 +143,11 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, *, m: int, n: int,
     args.m, args.n, args.k = m, n, k
     args.lda = k if lda is None else lda
     args.ldw = (n if w_layout == _lib.W_KN else k) if ldw is None else ldw
-    args.ldc = n if ldc is None else ldc
+    args.ldc = (n if out_tail is None else n_main) if ldc is None else ldc
+    if out_tail is not None:
+        if n_main is None:
+            raise ValueError("out_tail needs n_main")
+        args.out_tail_bf16, args.ldc_tail, args.n_main = _p(out_tail), out_tail.stride(0), n_main
     args.in_type = _lib.IN_INT8 if a.dtype == torch.int8 else _lib.IN_BF16
     args.out_kind = _OUT_KIND[out.dtype]
     args.w_layout = w_layout

@@ -57,6 +57,8 @@ SHAPES = [
     (77, 64, 2048), (130, 128, 8192), (2048, 4096, 256), (33, 8192, 256), (1000, 1024, 624), (5, 128, 128),
     # 8192 rows and more with a wide output: 256 x 256 tiles shared by CTA pairs
     (8200, 1536, 1024), (16384, 3072, 1024), (8192, 1000, 520), (9000, 4096, 256),
+    # a ragged last tile narrower than the tile: its MMAs cover 32 / 96 / 160 columns instead of 256
+    (300, 800, 256), (8200, 1056, 1024), (8200, 1120, 1024), (700, 3232, 1024), (8192, 3104, 1024),
 ]
 
 
@@ -241,6 +243,65 @@ def test_deferred_layer_norm_epilogues(ops, m) -> None:
     ops.gemm(hidden, z, scaled.t().contiguous().cuda(), m=m, n=f, k=d, activation="mish", w_layout=_lib.W_NK,
              ln_in=(stats, fold_c.cuda(), fold_d.cuda()), ln_eps=eps)
     torch.testing.assert_close(hidden.float().cpu(), want_h, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize(("m", "n_main", "n_tail", "k"), [(300, 256, 32, 512), (64, 256, 96, 256), (8300, 3072, 32, 1024),
+                                                         (8200, 512, 200, 1024), (1, 256, 8, 64)])
+def test_second_output_for_trailing_columns(ops, m, n_main, n_tail, k) -> None:
+    """Two projections of the same rows as one product: columns [0, n_main) to one matrix, the rest to a
+    second, narrower one (how smolgen's 32-wide compression rides on the QKV GEMM) - plain with bias and
+    activation, and with the LayerNorm of the rows folded into the epilogue.  Neither output may be written
+    outside its columns, and the pitch of each is its own."""
+    from lczero_triton_b200 import _lib
+
+    n = n_main + n_tail
+    g = _gen(190)
+    a = (torch.randn((m, k), generator=g) * 0.5).to(BF16)
+    w = (torch.randn((k, n), generator=g) * 0.2).to(BF16)
+    bias = (torch.randn(n, generator=g) * 0.5).to(BF16)
+    want = O.activate(O.matmul(a, w) + bias.float(), "mish")
+    main = torch.full((m + 1, n_main + 16), 7.0, dtype=BF16, device="cuda")
+    tail = torch.full((m + 1, n_tail + 8), 7.0, dtype=BF16, device="cuda")
+    ops.gemm(main[:m, :n_main], a.cuda(), w.t().contiguous().cuda(), m=m, n=n, k=k, bias=bias.cuda(), activation="mish",
+             w_layout=_lib.W_NK, ldc=n_main + 16, out_tail=tail[:m, :n_tail], n_main=n_main)
+    torch.testing.assert_close(main[:m, :n_main].float().cpu(), want[:, :n_main], rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(tail[:m, :n_tail].float().cpu(), want[:, n_main:], rtol=1e-2, atol=1e-2)
+    assert (main[:m, n_main:] == 7.0).all() and (main[m:] == 7.0).all()
+    assert (tail[:m, n_tail:] == 7.0).all() and (tail[m:] == 7.0).all()
+
+    # the same through the folded-LayerNorm epilogue (the form the forward pass uses)
+    eps = 1e-3
+    z = (torch.randn((m, k), generator=g) * 1.3 + 0.2).to(BF16)
+    gamma, beta = (1 + 0.1 * torch.randn(k, generator=g)).to(BF16), (0.1 * torch.randn(k, generator=g)).to(BF16)
+    w1 = (torch.randn((k, n), generator=g) * 0.05).to(BF16)
+    scaled = (w1.float() * gamma.float()[:, None]).to(BF16)
+    fold_c, fold_d = scaled.float().sum(dim=0), beta.float() @ w1.float() + bias.float()
+    want = O.matmul(O.layer_norm(z, torch.zeros(k), gamma, beta, "none", eps), w1) + bias.float()
+    stats = _partial_stats(z).cuda() if k % 64 == 0 else None
+    if stats is not None:
+        main.fill_(7.0)
+        tail.fill_(7.0)
+        ops.gemm(main[:m, :n_main], z.cuda(), scaled.t().contiguous().cuda(), m=m, n=n, k=k, w_layout=_lib.W_NK,
+                 ldc=n_main + 16, ln_in=(stats, fold_c.cuda(), fold_d.cuda()), ln_eps=eps, out_tail=tail[:m, :n_tail],
+                 n_main=n_main)
+        torch.testing.assert_close(main[:m, :n_main].float().cpu(), want[:, :n_main], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(tail[:m, :n_tail].float().cpu(), want[:, n_main:], rtol=2e-2, atol=2e-2)
+        assert (main[:m, n_main:] == 7.0).all() and (tail[:m, n_tail:] == 7.0).all()
+
+
+def test_second_output_is_refused_where_it_cannot_be_honoured(ops) -> None:
+    from lczero_triton_b200 import _lib
+
+    a = torch.zeros((64, 64), dtype=BF16, device="cuda")
+    w = torch.zeros((288, 64), dtype=BF16, device="cuda")
+    main = torch.zeros((64, 256), dtype=BF16, device="cuda")
+    tail = torch.zeros((64, 32), dtype=BF16, device="cuda")
+    with pytest.raises(_lib.Lc0B200Error):  # n_main must be a multiple of 256
+        ops.gemm(main[:, :128], a, w[:160], m=64, n=160, k=64, ldc=256, out_tail=tail, n_main=128)
+    with pytest.raises(_lib.Lc0B200Error):  # not on the CUDA-core kernel
+        ops.gemm(main, a, w, m=64, n=288, k=64, out_tail=tail, n_main=256, simt=True)
+    with pytest.raises(_lib.Lc0B200Error):  # not with the residual epilogue
+        ops.gemm(main, a, w, m=64, n=288, k=64, out_tail=tail, n_main=256, res_skip=main, res_alpha=1.0)
 
 
 def test_int8_gemm_residual_epilogue(ops) -> None:
