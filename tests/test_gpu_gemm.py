@@ -269,6 +269,16 @@ def test_second_output_for_trailing_columns(ops, m, n_main, n_tail, k) -> None:
     assert (main[:m, n_main:] == 7.0).all() and (main[m:] == 7.0).all()
     assert (tail[:m, n_tail:] == 7.0).all() and (tail[m:] == 7.0).all()
 
+    if n_tail % 8 == 0 and k % 64 == 0:
+        # the reference's [K, N] weight layout takes the same second output (whole-tile MMAs there)
+        main.fill_(7.0)
+        tail.fill_(7.0)
+        ops.gemm(main[:m, :n_main], a.cuda(), w.cuda(), m=m, n=n, k=k, bias=bias.cuda(), activation="mish",
+                 w_layout=_lib.W_KN, ldc=n_main + 16, out_tail=tail[:m, :n_tail], n_main=n_main)
+        torch.testing.assert_close(main[:m, :n_main].float().cpu(), want[:, :n_main], rtol=1e-2, atol=1e-2)
+        torch.testing.assert_close(tail[:m, :n_tail].float().cpu(), want[:, n_main:], rtol=1e-2, atol=1e-2)
+        assert (main[:m, n_main:] == 7.0).all() and (tail[:m, n_tail:] == 7.0).all()
+
     # the same through the folded-LayerNorm epilogue (the form the forward pass uses)
     eps = 1e-3
     z = (torch.randn((m, k), generator=g) * 1.3 + 0.2).to(BF16)
