@@ -621,6 +621,24 @@ _ADAPTERS: dict[str, Adapter] = {
         "elementwise.cu", ((_BF, "out"), (_CBF, "in"), (_CBF, "bias")), ("BATCH_COUNT", "ROWS", "CHANNELS", "ACTIVATION"),
         "add_bias_body(out, in, bias, (long long)BATCH_COUNT * ROWS * CHANNELS, CHANNELS, (long long)ROWS * CHANNELS, ACTIVATION);",
         _stream_launch(lambda c: c["BATCH_COUNT"] * c["ROWS"] * c["CHANNELS"])),
+    # K/matmul.py:57-116 on the CUDA cores (ABI order out, a, w of T/test_matmul.py:204-208; [K,N] weights): the
+    # form for the small and odd-shaped layers (output widths 1, 3, 4; rows that TMA cannot address).  The large
+    # layers belong on the tensor-core kernel, whose descriptors need the plan in TENSORMAP_NOTE.
+    "matmul_simt": Adapter(
+        "gemm_simt.cu", ((_BF, "out"), (_CBF, "a"), (_CBF, "w")), ("M", "N", "K"),
+        "SimtParams p = {out, a, w, nullptr, nullptr, nullptr, M, K, N, N, N, K, LC0B200_OUT_BF16, LC0B200_ACT_NONE, 1};\n"
+        "  gemm_simt_body<false>(p);",
+        lambda c: ((-(-c["N"] // 64), -(-c["M"] // 64), 1), (256, 1, 1), 0)),
+    # K/fused_qkv.py:132-183: three row-broadcast bias adds in one launch (ABI order of T/test_fused_qkv.py:95-109)
+    "fused_qkv_bias": Adapter(
+        "elementwise.cu",
+        ((_BF, "q_out"), (_CBF, "q_in"), (_CBF, "q_bias"), (_BF, "k_out"), (_CBF, "k_in"), (_CBF, "k_bias"),
+         (_BF, "v_out"), (_CBF, "v_in"), (_CBF, "v_bias")),
+        ("ROWS", "QUERY_WIDTH", "KEY_WIDTH", "VALUE_WIDTH"),
+        "QkvBiasParams p = {{q_out, k_out, v_out}, {q_in, k_in, v_in}, {q_bias, k_bias, v_bias},"
+        " {QUERY_WIDTH, KEY_WIDTH, VALUE_WIDTH}, ROWS};\n  fused_qkv_bias_body(p);",
+        lambda c: ((max(1, min(-(-c["ROWS"] * max(c["QUERY_WIDTH"], c["KEY_WIDTH"], c["VALUE_WIDTH"]) // 256), 148 * 32)),
+                    3, 1), (256, 1, 1), 0)),
     # K/copy_type_converted.py:26-34
     "copy_type_converted": Adapter(
         "elementwise.cu", (("float*", "out"), (_CBF, "in")), ("ELEMENTS",),

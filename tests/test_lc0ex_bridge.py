@@ -214,7 +214,7 @@ def test_compiled_artifacts_are_pointer_only_with_static_launch_metadata() -> No
     assert ln.dynamic_shared_memory_bytes == 0
     assert set(B.adapters()) >= {"layer_norm", "layer_norm_skip", "softmax_64", "qk_64", "expand_planes", "nchw_to_nhwc",
                                  "preprocess_attention_body", "input_gating", "add_vectors", "add_bias_batched",
-                                 "copy_type_converted", "policy_map", "promotion_logits"}
+                                 "copy_type_converted", "policy_map", "promotion_logits", "fused_qkv_bias", "matmul_simt"}
     with pytest.raises(ValueError):
         B.compile_kernel("softmax_64", {})
     # and it links: weights persistent, activations temporaries, one program
@@ -312,6 +312,21 @@ def test_element_wise_and_gather_artifacts_match_the_oracle() -> None:
             [out, x.cuda(), mult.cuda(), add.cuda()])
     want = O.input_gating(x.float().reshape(batch, 64, 128), mult.float(), add.float()).reshape(-1, 128)
     torch.testing.assert_close(out.float().cpu(), want, rtol=8e-3, atol=4e-3)
+    # three bias adds of different widths in one launch, in place (the reference's own widths 11 / 13 / 9)
+    widths = (11, 13, 9)
+    parts = [torch.randn((9, w), generator=gen).to(bf) for w in widths]
+    biases = [torch.randn(w, generator=gen).to(bf) for w in widths]
+    dev_parts, dev_biases = [t.cuda() for t in parts], [t.cuda() for t in biases]
+    _launch(B.compile_kernel("fused_qkv_bias", {"ROWS": 9, "QUERY_WIDTH": 11, "KEY_WIDTH": 13, "VALUE_WIDTH": 9}),
+            [t for trio in zip(dev_parts, dev_parts, dev_biases) for t in trio])
+    for got, x_, b_ in zip(dev_parts, parts, biases):
+        torch.testing.assert_close(got.float().cpu(), (x_.float() + b_.float()).to(bf).float(), rtol=0, atol=0)
+    # the CUDA-core matmul on the value head's last layer shape and on the reference's tail case 7 x 37 x 11
+    for m, k, n in ((batch, 128, 3), (7, 37, 11)):
+        a_, w_ = (torch.randn(shape, generator=gen).mul(0.3).to(bf) for shape in ((m, k), (k, n)))
+        product = torch.empty((m, n), dtype=bf, device="cuda")
+        _launch(B.compile_kernel("matmul_simt", {"M": m, "N": n, "K": k}), [product, a_.cuda(), w_.cuda()])
+        torch.testing.assert_close(product.float().cpu(), O.matmul(a_, w_), rtol=8e-3, atol=8e-3)
     # body_qk on the tensor cores, policy_map and the f32 widening (exact)
     heads = 4
     q, k = (torch.randn((batch, 64, heads * 32), generator=gen).mul(0.5).to(bf) for _ in range(2))
