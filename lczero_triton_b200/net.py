@@ -12,7 +12,8 @@ which is the reference's execution I/O contract (network.py:328-340, :1252-1257,
 ``_smolgen`` (:705-850), ``_attention`` (:853-1076), ``_ffn`` (:1079-1186),
 ``_policy_head`` (:1189-1356) and ``_dense_output_head`` (:1409-1550), with these
 fusions: bias/activation live in GEMM epilogues, QK^T + smolgen bias + softmax + PV
-is one kernel, Q/K/V is one GEMM over a concatenated weight, plane expansion is
+is one kernel, Q/K/V (and, where 3 x embedding is a multiple of 256, smolgen's compression as trailing
+columns with an output of their own) is one GEMM over a concatenated weight, plane expansion is
 folded into the two embedding gather kernels, and promotion + gather + f32
 widening is one kernel.
 
