@@ -36,7 +36,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 METRIC = "positions/sec at BT4 shape"
-CPU_SAMPLE_BATCH = 128  # positions per CPU step: about two seconds on 16 host threads
+CPU_SAMPLE_BATCH = 32  # positions per CPU step: the batch at which the CPU forward is fastest per position (8 and 128 are slower)
 
 
 def _peaks() -> tuple[dict, str]:
