@@ -347,8 +347,9 @@ def _attention_sweep(peaks: dict, peak_kind: str) -> list[dict]:
     from lczero_triton_b200 import ops
 
     gen = torch.Generator(device="cuda").manual_seed(0)
-    # tensor-pipe share of the kernel's cycles: ncu sm__pipe_tensor_cycles_active of the B = 512 capture
-    tensor_pipe_pct = {512: 10.4}
+    # tensor-pipe share of the kernel's cycles: ncu sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed,
+    # one-pass captures of this very kernel at the three sizes (a number taken under a profiler, so a constant here)
+    tensor_pipe_pct = {64: 5.7, 512: 10.4, 4096: 11.5}
     rows = []
     for b in (64, 512, 4096):
         h, d = 32, 1024
