@@ -5,23 +5,29 @@ emits as a graph of Triton kernels.  Nothing in the product package imports it;
 only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline
 legs may.  The reference has no forward function that runs on a CPU (it is a
 graph compiler whose executor lives in an lc0 fork that is not part of its
-tree), so the whole-network result is pinned op by op rather than end to end:
+tree), so the oracle is pinned three ways:
 
 * every op below follows the PyTorch reference written in the matching
   reference test (cited per function as ``T/<file>:<lines>``, relative to
   ``packages/lczero-triton/tests/``) or, where the test computes the expected
   value inline, the kernel source (``K/<file>``, relative to
   ``packages/lczero-triton/src/lczero_triton/bt4/kernels/``);
-* ``tests/golden/`` holds vectors produced by importing those reference test
-  functions, and ``tests/test_oracle_golden.py`` checks every op here against
-  them;
+  ``tests/golden/reference_vectors.npz`` holds vectors produced by importing
+  those reference test functions (``tests/test_oracle_golden.py``);
+* ``tests/golden/reference_kernel_outputs.npz`` holds the outputs of every
+  Triton kernel of the reference launched on a B200, and
+  ``tests/test_kernel_golden.py`` checks every op here against them;
 * the op ORDER follows ``packages/lczero-triton/src/lczero_triton/bt4/network.py``
-  (``N:<lines>``).
+  (``N:<lines>``), and ``tests/golden/reference_network_outputs.npz`` holds the
+  outputs of that graph itself (the reference's builder, kernels and allocation
+  plan, launched node by node on a B200) for a 4-layer, the BT3 and the BT4
+  shape; ``tests/test_network_golden.py`` checks ``forward`` here against them
+  (fp16 rounding apart: 2e-3 on BT4 policy logits).
 
-Parity status: per-op parity is pinned by the reference's own test references
-and known-answer cases.  End-to-end parity at the lc0 runtime boundary is
-unpinned (no executable reference forward exists to compare with).  The int8
-path has no reference counterpart at all; see ``oracle/int8_oracle.py``.
+Parity status: pinned per op and end to end for the fp16 graph the reference
+builds.  The lc0 runtime boundary itself (the fork that would load the
+executable) does not exist to compare with.  The int8 path has no reference
+counterpart at all; see ``oracle/int8_oracle.py``.
 
 ``round_to`` makes the oracle round every tensor the GPU path materialises in
 HBM to that dtype (a "rounded" oracle) so that kernel bugs can be told apart
