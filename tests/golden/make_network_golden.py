@@ -221,90 +221,115 @@ def build_program(cfg, batch: int, *, dry: bool):
     return builder, program, consumed
 
 
+class LoadedProgram:
+    """One program of the reference's executable on the current device: allocations made and filled, CUBINs
+    loaded, every node's launch arguments resolved to the reference linker's planned addresses."""
+
+    def __init__(self, builder, program, persistent: dict[str, torch.Tensor], inputs: dict[str, torch.Tensor], *,
+                 fill: int) -> None:
+        from cuda.bindings import driver
+        from lc0ex.buffer_builder import Buffer
+        from lc0ex.proto import lc0ex_pb2
+
+        self._driver = driver
+        ok = self._ok
+        buffers = builder._buffers
+        records = buffers._records
+        _, conflicts = builder._analyze_invocations(program)
+        plans = {True: buffers.plan(buffers.persistent_allocation(), {}), False: buffers.plan(program._allocation, conflicts)}
+        self._blobs = {kind: torch.full((plan.size_bytes + 256,), fill, dtype=torch.uint8, device="cuda")
+                       for kind, plan in plans.items()}
+
+        def view(buffer) -> torch.Tensor:
+            record = records[buffer]
+            kind = record.allocation.is_persistent()
+            offset = plans[kind].locations[buffer].offset
+            assert offset % record.alignment_bytes == 0 and offset + record.size_bytes <= plans[kind].size_bytes
+            return self._blobs[kind][offset:offset + record.size_bytes]
+
+        dtypes = {lc0ex_pb2.Buffer.DATA_TYPE_F32: torch.float32, lc0ex_pb2.Buffer.DATA_TYPE_F16: torch.float16,
+                  lc0ex_pb2.Buffer.DATA_TYPE_U64: torch.int64}
+        self.named: dict[str, torch.Tensor] = {}
+        for kind, source in ((True, persistent), (False, inputs)):
+            for buffer, external in plans[kind].external_buffers:
+                target = view(buffer).view(dtypes[external.dtype]).reshape(external.shape)
+                self.named[external.name] = target
+                if external.name in source:
+                    target.copy_(source[external.name].to(dtypes[external.dtype]).reshape(external.shape))
+                else:
+                    assert not kind and external.name.startswith("/output/"), external.name
+        missing = set(persistent) - set(self.named)
+        assert not missing, missing
+
+        self._modules: dict[bytes, object] = {}
+
+        def module_of(binary: bytes):
+            if binary not in self._modules:
+                self._modules[binary] = ok(driver.cuModuleLoadData(binary))
+            return self._modules[binary]
+
+        self._nodes = []
+        for invocation in program._invocations:
+            artifact = builder._kernels[invocation.kernel]
+            function = ok(driver.cuModuleGetFunction(module_of(artifact.binary_data), artifact.function.encode()))
+            if artifact.dynamic_shared_memory_bytes > 48 * 1024:
+                ok(driver.cuFuncSetAttribute(function,
+                                             driver.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                             artifact.dynamic_shared_memory_bytes))
+            arguments = iter(invocation.arguments)
+            pointers = []
+            for parameter in artifact.parameters:
+                if parameter == lc0ex_pb2.PARAMETER_TYPE_NULL_POINTER:
+                    pointers.append(0)
+                    continue
+                argument = next(arguments)
+                if isinstance(argument, Buffer):
+                    pointers.append(view(argument).data_ptr())
+                else:
+                    symbol = builder._symbols[argument]
+                    address, _size = ok(driver.cuModuleGetGlobal(module_of(symbol.binary_data), symbol.symbol_name.encode()))
+                    pointers.append(int(address))
+            assert next(arguments, None) is None
+            values = (ctypes.c_void_p * len(pointers))(*pointers)
+            slots = (ctypes.c_void_p * len(pointers))(*[ctypes.addressof(values) + i * ctypes.sizeof(ctypes.c_void_p)
+                                                        for i in range(len(pointers))])
+            self._nodes.append((function, artifact, values, slots))
+        counts = collections.Counter(node[1].function for node in self._nodes)
+        self.info = {"nodes": len(self._nodes), "kernels": len(builder._kernels),
+                     "execution_bytes": plans[False].size_bytes, "persistent_bytes": plans[True].size_bytes,
+                     "temporaries_bytes": sum(r.size_bytes for r in records.values() if r.external is None),
+                     "functions": dict(counts)}
+
+    def _ok(self, result):
+        assert result[0] == self._driver.CUresult.CUDA_SUCCESS, result[0]
+        return result[1] if len(result) == 2 else result[1:]
+
+    def launch(self) -> None:
+        """Every node in program order on torch's current stream (a valid order of the dependency graph)."""
+        stream = torch.cuda.current_stream().cuda_stream
+        for function, artifact, _values, slots in self._nodes:
+            self._ok(self._driver.cuLaunchKernel(function, *artifact.grid, *artifact.block,
+                                                 artifact.dynamic_shared_memory_bytes, stream, ctypes.addressof(slots), 0))
+
+    def outputs(self) -> dict[str, torch.Tensor]:
+        torch.cuda.synchronize()
+        return {name: tensor.clone().cpu() for name, tensor in self.named.items() if name.startswith("/output/")}
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        for module in self._modules.values():
+            self._ok(self._driver.cuModuleUnload(module))
+        self._modules, self._nodes = {}, []
+
+
 def run_program(builder, program, persistent: dict[str, torch.Tensor], inputs: dict[str, torch.Tensor], *,
                 fill: int) -> tuple[dict[str, torch.Tensor], dict]:
     """Launch the program's nodes in order at the reference linker's planned addresses."""
-    from cuda.bindings import driver
-    from lc0ex.buffer_builder import Buffer
-    from lc0ex.proto import lc0ex_pb2
-
-    def ok(result):
-        assert result[0] == driver.CUresult.CUDA_SUCCESS, result[0]
-        return result[1] if len(result) == 2 else result[1:]
-
-    buffers = builder._buffers
-    records = buffers._records
-    _, conflicts = builder._analyze_invocations(program)
-    plans = {True: buffers.plan(buffers.persistent_allocation(), {}), False: buffers.plan(program._allocation, conflicts)}
-    blobs = {kind: torch.full((plan.size_bytes + 256,), fill, dtype=torch.uint8, device="cuda") for kind, plan in plans.items()}
-
-    def view(buffer) -> torch.Tensor:
-        record = records[buffer]
-        kind = record.allocation.is_persistent()
-        offset = plans[kind].locations[buffer].offset
-        assert offset % record.alignment_bytes == 0 and offset + record.size_bytes <= plans[kind].size_bytes
-        return blobs[kind][offset:offset + record.size_bytes]
-
-    dtypes = {lc0ex_pb2.Buffer.DATA_TYPE_F32: torch.float32, lc0ex_pb2.Buffer.DATA_TYPE_F16: torch.float16,
-              lc0ex_pb2.Buffer.DATA_TYPE_U64: torch.int64}
-    named: dict[str, torch.Tensor] = {}
-    for kind, source in ((True, persistent), (False, inputs)):
-        for buffer, external in plans[kind].external_buffers:
-            target = view(buffer).view(dtypes[external.dtype]).reshape(external.shape)
-            named[external.name] = target
-            if external.name in source:
-                value = source[external.name].to(dtypes[external.dtype]).reshape(external.shape)
-                target.copy_(value)
-            else:
-                assert not kind and external.name.startswith("/output/"), external.name
-    missing = set(persistent) - set(named)
-    assert not missing, missing
-
-    modules: dict[bytes, object] = {}
-
-    def module_of(binary: bytes):
-        if binary not in modules:
-            modules[binary] = ok(driver.cuModuleLoadData(binary))
-        return modules[binary]
-
-    stream = torch.cuda.current_stream().cuda_stream
-    functions = []
-    for invocation in program._invocations:
-        artifact = builder._kernels[invocation.kernel]
-        function = ok(driver.cuModuleGetFunction(module_of(artifact.binary_data), artifact.function.encode()))
-        if artifact.dynamic_shared_memory_bytes > 48 * 1024:
-            ok(driver.cuFuncSetAttribute(function, driver.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
-                                         artifact.dynamic_shared_memory_bytes))
-        arguments = iter(invocation.arguments)
-        pointers = []
-        for parameter in artifact.parameters:
-            if parameter == lc0ex_pb2.PARAMETER_TYPE_NULL_POINTER:
-                pointers.append(0)
-                continue
-            argument = next(arguments)
-            if isinstance(argument, Buffer):
-                pointers.append(view(argument).data_ptr())
-            else:
-                symbol = builder._symbols[argument]
-                address, _size = ok(driver.cuModuleGetGlobal(module_of(symbol.binary_data), symbol.symbol_name.encode()))
-                pointers.append(int(address))
-        assert next(arguments, None) is None
-        values = (ctypes.c_void_p * len(pointers))(*pointers)
-        slots = (ctypes.c_void_p * len(pointers))(*[ctypes.addressof(values) + i * ctypes.sizeof(ctypes.c_void_p)
-                                                    for i in range(len(pointers))])
-        ok(driver.cuLaunchKernel(function, *artifact.grid, *artifact.block, artifact.dynamic_shared_memory_bytes, stream,
-                                 ctypes.addressof(slots), 0))
-        functions.append(artifact.function)
-    torch.cuda.synchronize()
-    outputs = {name: tensor.clone().cpu() for name, tensor in named.items() if name.startswith("/output/")}
-    for module in modules.values():
-        ok(driver.cuModuleUnload(module))
-    counts = collections.Counter(functions)
-    info = {"nodes": len(functions), "kernels": len(builder._kernels),
-            "execution_bytes": plans[False].size_bytes, "persistent_bytes": plans[True].size_bytes,
-            "temporaries_bytes": sum(r.size_bytes for r in records.values() if r.external is None),
-            "functions": dict(counts)}
-    return outputs, info
+    loaded = LoadedProgram(builder, program, persistent, inputs, fill=fill)
+    loaded.launch()
+    outputs = loaded.outputs()
+    loaded.close()
+    return outputs, loaded.info
 
 
 def main(argv: list[str]) -> None:
