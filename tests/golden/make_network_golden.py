@@ -3,7 +3,8 @@
 Run on a machine with a GPU and the unmodified reference package installed under ``baseline/_ref``:
 
     python tests/golden/make_network_golden.py [output.npz]        # needs a GPU
-    python tests/golden/make_network_golden.py --dry               # no GPU: walks the graph, launches nothing
+    python tests/golden/make_network_golden.py --dry               # no GPU: walks the graph, launches nothing,
+                                                                   # writes reference_program_plan.json
 
 The reference has no runtime of its own: ``lczero_triton.bt4.network`` appends kernel invocations to an
 ``lc0ex`` program and the lc0 fork that would run it is not in its tree.  This script is the missing forty
@@ -37,6 +38,7 @@ from __future__ import annotations
 
 import collections
 import ctypes
+import json
 import pathlib
 import sys
 import time
@@ -202,9 +204,33 @@ def build_program(cfg, batch: int, *, dry: bool):
             return types.SimpleNamespace(SetInParent=lambda: None)
 
     if dry:
-        calls = []
-        program.call = lambda kernel, *arguments, readonly=(): calls.append((kernel, arguments))  # type: ignore
-        kernels = types.SimpleNamespace(get=lambda compiler, spec: (compiler.__name__, spec))
+        # No GPU: nothing is compiled.  A kernel is a placeholder artifact named after its compile function,
+        # with as many pointer parameters as its first call passes; everything else (buffers, calls, read-only
+        # sets, dependency analysis, allocation plan) is the reference's code on the reference's graph.
+        from lc0ex.kernel_builder import KernelArtifact, KernelHandle
+        from lc0ex.proto import lc0ex_pb2
+
+        handles: dict[tuple, KernelHandle] = {}
+        names: dict[KernelHandle, str] = {}
+
+        def get(compiler, specialization):
+            handle = handles.setdefault((compiler, specialization), KernelHandle())
+            names[handle] = f"{compiler.__name__}#{list(handles).index((compiler, specialization))}"
+            return handle
+
+        recorded_call = program.call
+
+        def call(kernel, *arguments, readonly=()):
+            if kernel not in builder._kernels:
+                builder._kernels[kernel] = KernelArtifact(
+                    binary_format=lc0ex_pb2.Binary.FORMAT_CUBIN, binary_data=b"", function=names[kernel],
+                    parameters=(lc0ex_pb2.PARAMETER_TYPE_POINTER,) * len(arguments)
+                    + (lc0ex_pb2.PARAMETER_TYPE_NULL_POINTER,) * 2,
+                    grid=(1, 1, 1), block=(1, 1, 1), dynamic_shared_memory_bytes=0)
+            recorded_call(kernel, *arguments, readonly=readonly)
+
+        program.call = call  # type: ignore[method-assign]
+        kernels = types.SimpleNamespace(get=get)
         architecture = 100
     else:
         from lczero_triton.bt4.kernels._autotune import active_architecture
@@ -216,9 +242,37 @@ def build_program(cfg, batch: int, *, dry: bool):
     network._network(context, _Field("weights", cfg, shapes))
     unknown = [p for p in consumed if buffer_name(p) is None]
     assert not unknown, unknown
-    if dry:
-        program._dry_calls = calls  # type: ignore[attr-defined]
     return builder, program, consumed
+
+
+def dump_plan(builder, program) -> dict:
+    """The reference linker's view of one program, as plain data: every buffer in creation order, every call
+    with its buffer arguments and read-only set, the reduced dependencies (``_analyze_invocations``) and both
+    allocation plans (``BufferBuilder.plan``)."""
+    from lc0ex.buffer_builder import Buffer
+    from lc0ex.proto import lc0ex_pb2
+
+    buffers = builder._buffers
+    records = buffers._records
+    ids = {buffer: index for index, buffer in enumerate(records)}
+    dtype_names = {getattr(lc0ex_pb2.Buffer, "DATA_TYPE_" + n): n for n in ("F32", "F16", "U64", "U8", "BF16")}
+    dependencies, conflicts = builder._analyze_invocations(program)
+    plans = {"persistent": buffers.plan(buffers.persistent_allocation(), {}),
+             "execution": buffers.plan(program._allocation, conflicts)}
+    return {
+        "buffers": [{"persistent": r.allocation.is_persistent(), "size_bytes": r.size_bytes,
+                     "alignment_bytes": r.alignment_bytes, "writable": r.writable,
+                     "name": None if r.external is None else r.external.name,
+                     "shape": None if r.external is None else list(r.external.shape),
+                     "dtype": None if r.external is None else dtype_names[r.external.dtype]} for r in records.values()],
+        "calls": [{"kernel": builder._kernels[i.kernel].function,
+                   "arguments": [ids[a] if isinstance(a, Buffer) else -1 for a in i.arguments],
+                   "readonly": sorted(ids[b] for b in i.readonly)} for i in program._invocations],
+        "dependencies": [list(d) for d in dependencies],
+        "plans": {kind: {"size_bytes": plan.size_bytes, "alignment_bytes": plan.alignment_bytes,
+                         "offsets": {str(ids[b]): loc.offset for b, loc in plan.locations.items()}}
+                  for kind, plan in plans.items()},
+    }
 
 
 class LoadedProgram:
@@ -342,6 +396,7 @@ def main(argv: list[str]) -> None:
     from lczero_triton_b200 import weights as W
 
     out: dict[str, np.ndarray] = {}
+    plans: dict[str, dict] = {}
     for cfg_name, batch, seed in CASES:
         cfg = C.CONFIGS[cfg_name]
         started = time.time()
@@ -349,9 +404,10 @@ def main(argv: list[str]) -> None:
         if dry:
             declared = {e.name for _, e in builder._buffers.plan(builder._buffers.persistent_allocation(), {}).external_buffers}
             expected = set(W.weight_shapes(cfg)) | set(W.scalar_constants(cfg))
-            print(f"{cfg_name} batch {batch}: {len(program._dry_calls)} nodes, {len(consumed)} weight fields, "
+            print(f"{cfg_name} batch {batch}: {len(program._invocations)} nodes, {len(consumed)} weight fields, "
                   f"persistent names equal: {declared == expected}")
             assert declared == expected, (sorted(declared - expected), sorted(expected - declared))
+            plans[f"{cfg_name}_b{batch}"] = dump_plan(builder, program)
             continue
         built = time.time() - started
         weights = exact_in_both(W.random_weights(cfg, seed))
@@ -374,7 +430,12 @@ def main(argv: list[str]) -> None:
         out[f"{key}/nodes"] = np.array([info["nodes"], info["kernels"], info["execution_bytes"], info["temporaries_bytes"]])
         out[f"{key}/functions"] = np.array(sorted(f"{k} x{v}" for k, v in info["functions"].items()))
         np.savez_compressed(target, **out)  # after every case: a later case that fails keeps the earlier ones
-    if not dry:
+    if dry:
+        plan_target = pathlib.Path(__file__).with_name("reference_program_plan.json")
+        keep = {key: plans[key] for key in ("tiny_b5", "bt4_b2")}
+        plan_target.write_text(json.dumps(keep, separators=(",", ":")))
+        print(f"wrote {plan_target} ({plan_target.stat().st_size} bytes)")
+    else:
         print(f"wrote {target} ({target.stat().st_size} bytes, {len(out)} arrays)")
 
 
