@@ -113,6 +113,8 @@ __device__ __forceinline__ void load_head(uint8_t* stage, const AttnParams& p, l
 // HPB = consecutive heads streamed by one CTA.
 template <int HPB>
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   constexpr int kHeadsPerBlock = HPB;
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,6 +264,8 @@ __device__ __forceinline__ void softmax_64_body(bf16* out, const bf16* qk, const
 
 __global__ void __launch_bounds__(256) softmax_64_kernel(bf16* out, const bf16* qk, const bf16* smolgen,
                                                          long long rows) {
+  grid_dependency_release();
+  grid_dependency_wait();
   softmax_64_body(out, qk, smolgen, rows);
 }
 
@@ -340,6 +344,8 @@ __device__ __forceinline__ void qk_mma_body(const QkParams p) {
   }
 }
 __global__ void __launch_bounds__(128) qk_mma_kernel(const QkParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   qk_mma_body(p);
 }
 
@@ -354,6 +360,8 @@ struct BmmParams {
 };
 
 __global__ void __launch_bounds__(256) bmm_generic_kernel(const BmmParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const long long per = static_cast<long long>(p.m) * p.n;
   const long long total = p.batch_count * per;
   const float scale = (p.operation != LC0B200_BMM_BODY_ATTENTION_V && p.scale != nullptr)
@@ -397,7 +405,7 @@ __global__ void __launch_bounds__(256) bmm_generic_kernel(const BmmParams p) {
 
 int softmax_64(void* out, const void* qk, const void* smolgen, long long rows, cudaStream_t st) {
   const long long blocks = ceil_div_ll(rows, 8);
-  softmax_64_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(reinterpret_cast<bf16*>(out),
+  launch_dependent(softmax_64_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, st, reinterpret_cast<bf16*>(out),
                                                                  reinterpret_cast<const bf16*>(qk),
                                                                  reinterpret_cast<const bf16*>(smolgen), rows);
   return launch_status();
@@ -429,7 +437,7 @@ int attention(void* out, const void* q, const void* k, const void* v, const void
     if (allow_dynamic_smem(once, kernel, 2 * kStageBytes) != LC0B200_OK) return LC0B200_ERR_CUDA;
     const long long blocks = ceil_div_ll(p.items, heads_per_block);
     if (blocks > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
-    kernel<<<static_cast<unsigned>(blocks), 128, 2 * kStageBytes, st>>>(p);
+    launch_dependent(kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 2 * kStageBytes, st, p);
     return launch_status();
   };
   static PerDeviceOnce once16, once8, once4;
@@ -452,7 +460,7 @@ int batched_matmul(void* out, const void* a, const void* b, const void* scale, i
     p.depth = k;
     p.heads = heads;
     p.interleaved = operation == LC0B200_BMM_BODY_QK;
-    qk_mma_kernel<<<static_cast<unsigned>(batch_count), 128, 0, st>>>(p);
+    launch_dependent(qk_mma_kernel, dim3(static_cast<unsigned>(batch_count)), dim3(128), 0, st, p);
     return launch_status();
   }
   BmmParams p;
@@ -469,7 +477,7 @@ int batched_matmul(void* out, const void* a, const void* b, const void* scale, i
   long long blocks = ceil_div_ll(batch_count * m * n, 256);
   const long long cap = static_cast<long long>(sm_count()) * 32;
   if (blocks > cap) blocks = cap;
-  bmm_generic_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(p);
+  launch_dependent(bmm_generic_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, st, p);
   return launch_status();
 }
 

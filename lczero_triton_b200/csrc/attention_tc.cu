@@ -84,6 +84,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  grid_dependency_release();
   if (threadIdx.x == 0) {
     abort_flag_storage = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -123,6 +124,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   ptx::tc_fence_after_sync();
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  grid_dependency_wait();  // set-up done; Q, K, V and the bias come from the kernels before this one
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -390,7 +392,7 @@ int attention_tc(void* out, const void* q, const void* k, const void* v, const v
   p.status = device_status_words();
   if (p.status == nullptr) return LC0B200_ERR_CUDA;
   const long long grid = p.pairs < sm_count() ? p.pairs : sm_count();
-  attention_tc_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(mq, mk, mv, mb, mo, p);
+  launch_dependent(attention_tc_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), kSmemBytes, st, mq, mk, mv, mb, mo, p);
   return launch_status();
 }
 

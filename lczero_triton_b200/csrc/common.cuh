@@ -118,6 +118,55 @@ inline int allow_dynamic_smem(PerDeviceOnce& once, Kernel kernel, int bytes) {
   return LC0B200_OK;
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_dependent() may be scheduled while the
+// kernel before it on the stream is still running: its blocks become resident as soon as every block of the
+// predecessor has executed grid_dependency_release() (or exited) and resources are free, and they run up to
+// grid_dependency_wait(), which returns once the predecessor grid has COMPLETED and its writes are visible.
+// What comes before the wait (launch latency, barrier and tensor-memory set-up, descriptor prefetch) thereby
+// overlaps the predecessor's tail.  The rule every kernel here follows: release first, wait before the first
+// access to global memory (reads of what the predecessor wrote, and writes the predecessor may still read).
+// Waiting chains: kernel N+1 completes only after kernel N has, so data of kernel N-1 is visible too.
+// Launched the ordinary way (or after a copy) both instructions return at once.  Stream capture records the
+// edge as a programmatic one.  Every kernel of the library follows the rule; launch_dependent() asks for the
+// overlap only for grids of at most kMaxDependentBlocks blocks.  A streaming kernel with one small block per
+// row has 65536 and more blocks at the large batches, and there the programmatic launch costs more than its
+// overlap gives (int8 forward at batch 4096: 5 % slower), while at small batches it is where most of the
+// launches are.  LC0B200_PDL=0 compiles the ordinary launches back in (A/B measurements).
+#ifndef LC0B200_PDL
+#define LC0B200_PDL 1
+#endif
+__device__ __forceinline__ void grid_dependency_release() {
+#if LC0B200_PDL
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+#if LC0B200_PDL
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+constexpr unsigned long long kMaxDependentBlocks = 16384;
+inline cudaLaunchAttribute dependent_launch_attribute(bool allowed = true) {
+  cudaLaunchAttribute a = {};
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = (LC0B200_PDL && allowed) ? 1 : 0;
+  return a;
+}
+template <typename... Params, typename... Args>
+inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  const unsigned long long blocks = 1ull * grid.x * grid.y * grid.z;
+  cudaLaunchAttribute attribute = dependent_launch_attribute(blocks <= kMaxDependentBlocks);
+  cfg.attrs = &attribute;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);  // the error stays in the thread's slot
+}
+
 // Status of the `<<<>>>` launch just made by this thread.  cudaGetLastError also CLEARS the thread's
 // error slot, so one failed launch is reported once, by the call that made it, and neither by later
 // calls of this library nor by the host framework's own launch checks.

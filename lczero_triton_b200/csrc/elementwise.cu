@@ -37,6 +37,8 @@ __device__ __forceinline__ void expand_planes_body(bf16* __restrict__ out, const
 }
 __global__ void expand_planes_kernel(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
                                      const float* __restrict__ values, long long plane_count) {
+  grid_dependency_release();
+  grid_dependency_wait();
   expand_planes_body(out, masks, values, plane_count);
 }
 
@@ -54,6 +56,8 @@ __device__ __forceinline__ void nchw_to_nhwc_body(bf16* __restrict__ out, const 
 }
 __global__ void nchw_to_nhwc_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, long long total,
                                     int input_channels, int output_channels, int hw) {
+  grid_dependency_release();
+  grid_dependency_wait();
   nchw_to_nhwc_body(out, in, total, input_channels, output_channels, hw);
 }
 
@@ -75,6 +79,8 @@ __device__ __forceinline__ void preprocess_attention_body_body(bf16* __restrict_
 __global__ void preprocess_attention_body_kernel(bf16* __restrict__ out, const bf16* __restrict__ planes,
                                                  const bf16* __restrict__ encoding, long long total,
                                                  int input_channels, int encoding_channels) {
+  grid_dependency_release();
+  grid_dependency_wait();
   preprocess_attention_body_body(out, planes, encoding, total, input_channels, encoding_channels);
 }
 
@@ -90,12 +96,16 @@ __device__ __forceinline__ void input_gating_body(bf16* out, const bf16* in, con
 }
 __global__ void input_gating_kernel(bf16* out, const bf16* in, const bf16* __restrict__ mult,
                                     const bf16* __restrict__ add, long long total, long long gate_elements) {
+  grid_dependency_release();
+  grid_dependency_wait();
   input_gating_body(out, in, mult, add, total, gate_elements);
 }
 
 // Same, eight channels per thread with 16-byte accesses (gate_elements a multiple of 8).
 __global__ void input_gating_vec_kernel(uint4* out, const uint4* in, const uint4* __restrict__ mult,
                                         const uint4* __restrict__ add, long long groups, long long gate_groups) {
+  grid_dependency_release();
+  grid_dependency_wait();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < groups;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long g = i % gate_groups;
@@ -125,6 +135,8 @@ __device__ __forceinline__ void add_bias_body(bf16* out, const bf16* in, const b
 }
 __global__ void add_bias_kernel(bf16* out, const bf16* in, const bf16* __restrict__ bias, long long total,
                                 int channels, long long elements_per_batch, int activation) {
+  grid_dependency_release();
+  grid_dependency_wait();
   add_bias_body(out, in, bias, total, channels, elements_per_batch, activation);
 }
 
@@ -149,6 +161,8 @@ __device__ __forceinline__ void fused_qkv_bias_body(const QkvBiasParams p) {
   }
 }
 __global__ void fused_qkv_bias_kernel(const QkvBiasParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   fused_qkv_bias_body(p);
 }
 
@@ -160,6 +174,8 @@ __device__ __forceinline__ void widen_body(float* __restrict__ out, const bf16* 
   }
 }
 __global__ void widen_kernel(float* __restrict__ out, const bf16* __restrict__ in, long long total) {
+  grid_dependency_release();
+  grid_dependency_wait();
   widen_body(out, in, total);
 }
 
@@ -176,12 +192,16 @@ __device__ __forceinline__ void policy_map_body(bf16* __restrict__ out, const bf
 }
 __global__ void policy_map_kernel(bf16* __restrict__ out, const bf16* __restrict__ in,
                                   const int32_t* __restrict__ table, long long total, int in_count, int out_count) {
+  grid_dependency_release();
+  grid_dependency_wait();
   policy_map_body(out, in, table, total, in_count, out_count);
 }
 
 // dst[c, r] = src[r, c] through a padded shared-memory tile.
 template <typename T>
 __global__ void transpose_kernel(T* __restrict__ dst, const T* __restrict__ src, int rows, int cols) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ T tile[32][33];
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
@@ -199,6 +219,8 @@ __global__ void transpose_kernel(T* __restrict__ dst, const T* __restrict__ src,
 // (expand_planes.py + nchw_to_nhwc.py; network.py:458-484).
 __global__ void embed_position_input_kernel(bf16* __restrict__ out, const uint64_t* __restrict__ masks,
                                             const float* __restrict__ values, long long total) {
+  grid_dependency_release();
+  grid_dependency_wait();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int c = static_cast<int>(i % 12);
@@ -218,6 +240,8 @@ __global__ void __launch_bounds__(kBlock) embed_concat_kernel(bf16* __restrict__
                                                               const uint64_t* __restrict__ masks,
                                                               const float* __restrict__ values,
                                                               const bf16* __restrict__ position, int enc) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ uint64_t s_mask[112];
   __shared__ uint16_t s_val[112];
   const long long b = blockIdx.x;
@@ -288,6 +312,8 @@ template <int GROUPS>
 __global__ void __launch_bounds__(kQuantWarps * 32) quantize_rows_held_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
                                                                               const bf16* __restrict__ in, long long rows,
                                                                               int width, long long ld_in) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kQuantWarps) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -319,6 +345,8 @@ __global__ void __launch_bounds__(kQuantWarps * 32) quantize_rows_held_kernel(in
 __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(int8_t* __restrict__ out, float* __restrict__ scale,
                                                                const bf16* __restrict__ in, long long rows,
                                                                int width, long long ld_in) {
+  grid_dependency_release();
+  grid_dependency_wait();
   constexpr int kHeld = 8;  // 16-byte groups a lane keeps in registers: 8 * 32 lanes * 8 values = 2048 columns
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kBlock / 32) + (threadIdx.x >> 5);
@@ -370,14 +398,14 @@ __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(int8_t* __restric
 #define LC0_STREAM(s) reinterpret_cast<cudaStream_t>(s)
 
 int expand_planes(void* out, const uint64_t* masks, const float* values, long long plane_count, cudaStream_t st) {
-  expand_planes_kernel<<<grid_for(plane_count * 64), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out), masks, values,
+  launch_dependent(expand_planes_kernel, dim3(grid_for(plane_count * 64)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out), masks, values,
                                                                      plane_count);
   return launch_status();
 }
 
 int nchw_to_nhwc(void* out, const void* in, int batch, int in_ch, int out_ch, int hw, cudaStream_t st) {
   const long long total = static_cast<long long>(batch) * hw * out_ch;
-  nchw_to_nhwc_kernel<<<grid_for(total), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out),
+  launch_dependent(nchw_to_nhwc_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out),
                                                           reinterpret_cast<const bf16*>(in), total, in_ch, out_ch, hw);
   return launch_status();
 }
@@ -385,7 +413,7 @@ int nchw_to_nhwc(void* out, const void* in, int batch, int in_ch, int out_ch, in
 int preprocess_attention_body(void* out, const void* planes, const void* enc, int batch, int in_ch, int enc_ch,
                               cudaStream_t st) {
   const long long total = static_cast<long long>(batch) * 64 * (in_ch + enc_ch);
-  preprocess_attention_body_kernel<<<grid_for(total), kBlock, 0, st>>>(
+  launch_dependent(preprocess_attention_body_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, 
       reinterpret_cast<bf16*>(out), reinterpret_cast<const bf16*>(planes), reinterpret_cast<const bf16*>(enc), total,
       in_ch, enc_ch);
   return launch_status();
@@ -396,12 +424,12 @@ int input_gating(void* out, const void* in, const void* mult, const void* add, i
   const long long gate = static_cast<long long>(squares) * channels;
   const long long total = gate * batch;
   if (gate % 8 == 0 && aligned16(out) && aligned16(in) && aligned16(mult) && aligned16(add)) {
-    input_gating_vec_kernel<<<grid_for(total / 8), kBlock, 0, st>>>(
+    launch_dependent(input_gating_vec_kernel, dim3(grid_for(total / 8)), dim3(kBlock), 0, st, 
         reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(in), reinterpret_cast<const uint4*>(mult),
         reinterpret_cast<const uint4*>(add), total / 8, gate / 8);
     return launch_status();
   }
-  input_gating_kernel<<<grid_for(total), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out),
+  launch_dependent(input_gating_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out),
                                                           reinterpret_cast<const bf16*>(in),
                                                           reinterpret_cast<const bf16*>(mult),
                                                           reinterpret_cast<const bf16*>(add), total, gate);
@@ -410,7 +438,7 @@ int input_gating(void* out, const void* in, const void* mult, const void* add, i
 
 int add_bias(void* out, const void* in, const void* bias, long long total, int channels, long long per_batch,
              int activation, cudaStream_t st) {
-  add_bias_kernel<<<grid_for(total), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out), reinterpret_cast<const bf16*>(in),
+  launch_dependent(add_bias_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out), reinterpret_cast<const bf16*>(in),
                                                       reinterpret_cast<const bf16*>(bias), total, channels, per_batch,
                                                       activation);
   return launch_status();
@@ -429,19 +457,19 @@ int fused_qkv_bias(void* const out[3], const void* const in[3], const void* cons
   }
   p.rows = rows;
   dim3 grid(grid_for(rows * wmax), 3);
-  fused_qkv_bias_kernel<<<grid, kBlock, 0, st>>>(p);
+  launch_dependent(fused_qkv_bias_kernel, dim3(grid), dim3(kBlock), 0, st, p);
   return launch_status();
 }
 
 int widen(float* out, const void* in, long long total, cudaStream_t st) {
-  widen_kernel<<<grid_for(total), kBlock, 0, st>>>(out, reinterpret_cast<const bf16*>(in), total);
+  launch_dependent(widen_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, out, reinterpret_cast<const bf16*>(in), total);
   return launch_status();
 }
 
 int policy_map(void* out, const void* in, const int32_t* table, int batch, int in_count, int out_count,
                cudaStream_t st) {
   const long long total = static_cast<long long>(batch) * out_count;
-  policy_map_kernel<<<grid_for(total), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out),
+  launch_dependent(policy_map_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out),
                                                         reinterpret_cast<const bf16*>(in), table, total, in_count,
                                                         out_count);
   return launch_status();
@@ -450,10 +478,10 @@ int policy_map(void* out, const void* in, const int32_t* table, int batch, int i
 int transpose(void* dst, const void* src, int rows, int cols, int element_size, cudaStream_t st) {
   dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
   if (element_size == 1) {
-    transpose_kernel<uint8_t><<<grid, block, 0, st>>>(reinterpret_cast<uint8_t*>(dst),
+    launch_dependent(transpose_kernel<uint8_t>, dim3(grid), dim3(block), 0, st, reinterpret_cast<uint8_t*>(dst),
                                                       reinterpret_cast<const uint8_t*>(src), rows, cols);
   } else {
-    transpose_kernel<uint16_t><<<grid, block, 0, st>>>(reinterpret_cast<uint16_t*>(dst),
+    launch_dependent(transpose_kernel<uint16_t>, dim3(grid), dim3(block), 0, st, reinterpret_cast<uint16_t*>(dst),
                                                        reinterpret_cast<const uint16_t*>(src), rows, cols);
   }
   return launch_status();
@@ -461,13 +489,13 @@ int transpose(void* dst, const void* src, int rows, int cols, int element_size, 
 
 int embed_position_input(void* out, const uint64_t* masks, const float* values, int batch, cudaStream_t st) {
   const long long total = static_cast<long long>(batch) * 64 * 12;
-  embed_position_input_kernel<<<grid_for(total), kBlock, 0, st>>>(reinterpret_cast<bf16*>(out), masks, values, total);
+  launch_dependent(embed_position_input_kernel, dim3(grid_for(total)), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out), masks, values, total);
   return launch_status();
 }
 
 int embed_concat(void* out, const uint64_t* masks, const float* values, const void* position, int batch, int enc,
                  cudaStream_t st) {
-  embed_concat_kernel<<<batch, kBlock, 0, st>>>(reinterpret_cast<bf16*>(out), masks, values,
+  launch_dependent(embed_concat_kernel, dim3(batch), dim3(kBlock), 0, st, reinterpret_cast<bf16*>(out), masks, values,
                                                 reinterpret_cast<const bf16*>(position), enc);
   return launch_status();
 }
@@ -483,13 +511,13 @@ int quantize_rows(void* out, float* scale, const void* in, long long rows, int w
                     rows <= 0x7FFFFFFFLL;
   if (held) {
     const int g = (width + 255) / 256;
-    if (g <= 1) quantize_rows_held_kernel<1><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
-    else if (g <= 2) quantize_rows_held_kernel<2><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
-    else if (g <= 4) quantize_rows_held_kernel<4><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
-    else if (g <= 6) quantize_rows_held_kernel<6><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
-    else quantize_rows_held_kernel<8><<<held_blocks, kHeldThreads, 0, st>>>(q, scale, x, rows, width, ld_in);
+    if (g <= 1) launch_dependent(quantize_rows_held_kernel<1>, dim3(held_blocks), dim3(kHeldThreads), 0, st, q, scale, x, rows, width, ld_in);
+    else if (g <= 2) launch_dependent(quantize_rows_held_kernel<2>, dim3(held_blocks), dim3(kHeldThreads), 0, st, q, scale, x, rows, width, ld_in);
+    else if (g <= 4) launch_dependent(quantize_rows_held_kernel<4>, dim3(held_blocks), dim3(kHeldThreads), 0, st, q, scale, x, rows, width, ld_in);
+    else if (g <= 6) launch_dependent(quantize_rows_held_kernel<6>, dim3(held_blocks), dim3(kHeldThreads), 0, st, q, scale, x, rows, width, ld_in);
+    else launch_dependent(quantize_rows_held_kernel<8>, dim3(held_blocks), dim3(kHeldThreads), 0, st, q, scale, x, rows, width, ld_in);
   } else {
-    quantize_rows_kernel<<<blocks, kBlock, 0, st>>>(q, scale, x, rows, width, ld_in);
+    launch_dependent(quantize_rows_kernel, dim3(blocks), dim3(kBlock), 0, st, q, scale, x, rows, width, ld_in);
   }
   return launch_status();
 }

@@ -480,6 +480,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t vec_base = bar_base + 512;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 4 - smem_base));
   static_assert(16 * 8 + 32 + 8 * 8 + 16 + 8 <= 512, "barrier area too small");
+  grid_dependency_release();  // the next kernel on the stream may be scheduled as blocks of this one retire
   if ((smem_base & 1023u) != 0u) {  // never seen; refuse loudly rather than mis-swizzle
     if (threadIdx.x == 0 && atomicCAS(&p.status[0], 0u, kDeviceSmemMisaligned) == 0u) p.status[1] = smem_base;
     return;
@@ -532,6 +533,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   ptx::tc_fence_after_sync();
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  // Barriers, tensor memory and descriptors are ready; nothing in global memory has been touched.  From here
+  // on every role reads or writes what the previous kernel on the stream produced or may still be reading.
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (every CTA loads its own operands)
@@ -991,13 +995,14 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CTAS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0] = dependent_launch_attribute();
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = CTAS;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = CTAS == 2 ? 1 : 0;
+  cfg.numAttrs = CTAS == 2 ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kernel, map_a, map_w, map_out, map_skip, map_tail, p) != cudaSuccess) {
     (void)cudaGetLastError();  // reported here; do not leave it for an unrelated later call
     return LC0B200_ERR_CUDA;

@@ -174,11 +174,15 @@ __device__ __forceinline__ void layer_norm_warp_body(const LnParams& p) {
 
 template <int GROUPS, int ACT, int SKIP, int QUANT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layer_norm_warp_kernel(const LnParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   layer_norm_warp_body<GROUPS, ACT, SKIP, QUANT>(p);
 }
 
 // One CTA per row, row cached in shared memory as fp32 (any width, any alignment).
 __global__ void __launch_bounds__(256) layer_norm_block_kernel(const LnParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   extern __shared__ float row_cache[];
   __shared__ float red[32];
   const long long row = blockIdx.x;
@@ -228,6 +232,8 @@ __global__ void __launch_bounds__(256) layer_norm_block_kernel(const LnParams p)
 // the one-warp kernel: fixed at compile time for what the forward pass runs (swish, no skip), -1 = run time.
 template <int GROUPS, int ACT, int SKIP>
 __global__ void __launch_bounds__(256) layer_norm_wide_kernel(const LnParams p) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ float red[2][8];
   const long long row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -326,17 +332,17 @@ int launch_warp(const LnParams& p, cudaStream_t st) {
   const bool quant = p.q_out != nullptr;
   // The combinations the forward pass runs, decided at compile time; the rest at run time.
   if (p.activation == LC0B200_ACT_NONE && p.has_skip && !quant) {
-    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 0><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 0>, dim3(blocks), dim3(kThreads), 0, st, p);
   } else if (p.activation == LC0B200_ACT_NONE && p.has_skip && quant) {
-    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 1><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 1, 1>, dim3(blocks), dim3(kThreads), 0, st, p);
   } else if (p.activation == LC0B200_ACT_NONE && !p.has_skip && !quant) {
-    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, LC0B200_ACT_NONE, 0, 0>, dim3(blocks), dim3(kThreads), 0, st, p);
   } else if (p.activation == LC0B200_ACT_MISH && !p.has_skip && !quant) {
-    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_MISH, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, LC0B200_ACT_MISH, 0, 0>, dim3(blocks), dim3(kThreads), 0, st, p);
   } else if (p.activation == LC0B200_ACT_SWISH && !p.has_skip && !quant) {
-    layer_norm_warp_kernel<GROUPS, LC0B200_ACT_SWISH, 0, 0><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, LC0B200_ACT_SWISH, 0, 0>, dim3(blocks), dim3(kThreads), 0, st, p);
   } else {
-    layer_norm_warp_kernel<GROUPS, -1, -1, -1><<<blocks, kThreads, 0, st>>>(p);
+    launch_dependent(layer_norm_warp_kernel<GROUPS, -1, -1, -1>, dim3(blocks), dim3(kThreads), 0, st, p);
   }
   return launch_status();
 }
@@ -350,6 +356,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 normalize_quantize_kernel(int8_t* __restrict__ q_out, float* __restrict__ q_scale, const bf16* __restrict__ z,
                           const float2* __restrict__ stats, int parts, const bf16* __restrict__ gamma,
                           const bf16* __restrict__ beta, long long rows, int width, float epsilon) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * static_cast<long long>(kWarpsPerBlock) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -428,10 +436,10 @@ int normalize_quantize_rows(void* q_out, float* q_scale, const void* z, const fl
   const auto* ga = reinterpret_cast<const bf16*>(gamma);
   const auto* be = reinterpret_cast<const bf16*>(beta);
   const int g = (width + 255) / 256;
-  if (g <= 1) normalize_quantize_kernel<1><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
-  else if (g <= 2) normalize_quantize_kernel<2><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
-  else if (g <= 4) normalize_quantize_kernel<4><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
-  else normalize_quantize_kernel<8><<<blocks, block, 0, st>>>(qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  if (g <= 1) launch_dependent(normalize_quantize_kernel<1>, dim3(blocks), dim3(block), 0, st, qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else if (g <= 2) launch_dependent(normalize_quantize_kernel<2>, dim3(blocks), dim3(block), 0, st, qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else if (g <= 4) launch_dependent(normalize_quantize_kernel<4>, dim3(blocks), dim3(block), 0, st, qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
+  else launch_dependent(normalize_quantize_kernel<8>, dim3(blocks), dim3(block), 0, st, qo, q_scale, zz, st2, parts, ga, be, rows, width, epsilon);
   return launch_status();
 }
 
@@ -477,14 +485,14 @@ int layer_norm(void* out, const void* in, const void* bias, const void* skip, co
     const unsigned grid = static_cast<unsigned>(rows);
     const bool swish_plain = activation == LC0B200_ACT_SWISH && !has_skip;  // the smolgen LayerNorms
     if (g <= 2) {
-      if (swish_plain) layer_norm_wide_kernel<2, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
-      else layer_norm_wide_kernel<2, -1, -1><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) launch_dependent(layer_norm_wide_kernel<2, LC0B200_ACT_SWISH, 0>, dim3(grid), dim3(256), 0, st, p);
+      else launch_dependent(layer_norm_wide_kernel<2, -1, -1>, dim3(grid), dim3(256), 0, st, p);
     } else if (g <= 4) {
-      if (swish_plain) layer_norm_wide_kernel<4, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
-      else layer_norm_wide_kernel<4, -1, -1><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) launch_dependent(layer_norm_wide_kernel<4, LC0B200_ACT_SWISH, 0>, dim3(grid), dim3(256), 0, st, p);
+      else launch_dependent(layer_norm_wide_kernel<4, -1, -1>, dim3(grid), dim3(256), 0, st, p);
     } else {
-      if (swish_plain) layer_norm_wide_kernel<8, LC0B200_ACT_SWISH, 0><<<grid, 256, 0, st>>>(p);
-      else layer_norm_wide_kernel<8, -1, -1><<<grid, 256, 0, st>>>(p);
+      if (swish_plain) launch_dependent(layer_norm_wide_kernel<8, LC0B200_ACT_SWISH, 0>, dim3(grid), dim3(256), 0, st, p);
+      else launch_dependent(layer_norm_wide_kernel<8, -1, -1>, dim3(grid), dim3(256), 0, st, p);
     }
     return launch_status();
   }
@@ -497,7 +505,7 @@ int layer_norm(void* out, const void* in, const void* bias, const void* skip, co
     }
   }
   if (rows > 0x7FFFFFFFLL) return LC0B200_ERR_BAD_SHAPE;
-  layer_norm_block_kernel<<<static_cast<unsigned>(rows), 256, smem, st>>>(p);
+  launch_dependent(layer_norm_block_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), smem, st, p);
   return launch_status();
 }
 

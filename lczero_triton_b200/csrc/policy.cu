@@ -52,12 +52,16 @@ __device__ __forceinline__ void promotion_logits_body(bf16* records, const bf16*
 }
 __global__ void __launch_bounds__(256) promotion_logits_kernel(bf16* records, const bf16* __restrict__ keys,
                                                                const bf16* __restrict__ w, int width) {
+  grid_dependency_release();
+  grid_dependency_wait();
   promotion_logits_body(records, keys, w, width);
 }
 
 __global__ void __launch_bounds__(256) policy_tail_kernel(float* __restrict__ out, const bf16* __restrict__ records,
                                                           const bf16* __restrict__ keys, const bf16* __restrict__ w,
                                                           const int32_t* __restrict__ table, int width) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ float offs[8][3];
   const long long b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,6 +93,8 @@ __global__ void __launch_bounds__(256) output_probabilities_kernel(float* __rest
                                                                    const float* __restrict__ policy_logits,
                                                                    const float* __restrict__ wdl_logits,
                                                                    const uint8_t* __restrict__ legal, int policy_size) {
+  grid_dependency_release();
+  grid_dependency_wait();
   __shared__ float red[8];
   __shared__ float bcast;
   const long long b = blockIdx.x;
@@ -152,20 +158,20 @@ __global__ void __launch_bounds__(256) output_probabilities_kernel(float* __rest
 
 int output_probabilities(float* policy_probs, float* wdl_probs, float* q_d, const float* policy_logits,
                          const float* wdl_logits, const uint8_t* legal, int batch, int policy_size, cudaStream_t st) {
-  output_probabilities_kernel<<<batch, 256, 0, st>>>(policy_probs, wdl_probs, q_d, policy_logits, wdl_logits, legal,
+  launch_dependent(output_probabilities_kernel, dim3(batch), dim3(256), 0, st, policy_probs, wdl_probs, q_d, policy_logits, wdl_logits, legal,
                                                      policy_size);
   return launch_status();
 }
 
 int promotion_logits(void* records, const void* keys, const void* w, int batch, int width, cudaStream_t st) {
-  promotion_logits_kernel<<<batch, 256, 0, st>>>(reinterpret_cast<bf16*>(records), reinterpret_cast<const bf16*>(keys),
+  launch_dependent(promotion_logits_kernel, dim3(batch), dim3(256), 0, st, reinterpret_cast<bf16*>(records), reinterpret_cast<const bf16*>(keys),
                                                  reinterpret_cast<const bf16*>(w), width);
   return launch_status();
 }
 
 int policy_tail(float* out, const void* records, const void* keys, const void* w, const int32_t* table, int batch,
                 int width, cudaStream_t st) {
-  policy_tail_kernel<<<batch, 256, 0, st>>>(out, reinterpret_cast<const bf16*>(records),
+  launch_dependent(policy_tail_kernel, dim3(batch), dim3(256), 0, st, out, reinterpret_cast<const bf16*>(records),
                                             reinterpret_cast<const bf16*>(keys), reinterpret_cast<const bf16*>(w),
                                             table, width);
   return launch_status();
