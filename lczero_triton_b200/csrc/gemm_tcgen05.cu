@@ -895,8 +895,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   // Neither CTA of a pair may leave while the other can still signal its barriers or read its smem.
   if (CTAS == 2) ptx::cluster_sync();
-  if (threadIdx.x == 0) {
-  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     if (CTAS == 2) {
