@@ -57,6 +57,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--profile-one", action="store_true",
+                    help="bracket ONE plain forward of each side with cudaProfilerStart/Stop (for a profiler run with "
+                         "--profile-from-start off: the launch lists of the two programs, nothing else)")
     args = ap.parse_args()
     if not (ROOT / "baseline" / "_ref" / "lczero_triton").exists():
         print(json.dumps({"unavailable": "baseline/_ref holds no reference install"}))
@@ -89,6 +92,12 @@ def main() -> None:
     assert all(bool(torch.isfinite(t).all()) for t in reference.values())
     ms_graph = _time(_captured(loaded.launch), args.iters)
     ms_plain = _time(loaded.launch, args.iters)
+    if args.profile_one:
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStart()
+        loaded.launch()
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
     print(json.dumps({"impl": "reference graph (Triton kernels, its allocation plan)", "config": args.config,
                       "batch": args.batch, "dtype": "fp16", "nodes": loaded.info["nodes"],
                       "kernel_specialisations": loaded.info["kernels"], "graph_build_s": round(built, 1),
@@ -104,6 +113,12 @@ def main() -> None:
         outs = [x.float().cpu() for x in net.forward(masks, values)]
         ms_graph = _time(_captured(lambda: net.forward(masks, values)), args.iters)
         ms_plain = _time(lambda: net.forward(masks, values), args.iters)
+        if args.profile_one and mode == "bf16":
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStart()
+            net.forward(masks, values)
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
         differences = {name: float((outs[i].reshape(args.batch, -1) - reference[f"/output/{name}"].float().reshape(args.batch, -1))
                                    .abs().max()) for i, name in enumerate(("policy", "wdl", "mlh"))}
         print(json.dumps({"impl": f"this library, C network object, {mode}", "config": args.config, "batch": args.batch,
