@@ -17,6 +17,11 @@
  *    from several threads.  A failed kernel launch is reported by the call that made it
  *    and cleared; composite entry points (fused_qkv_projection, linear_int8*, net_forward)
  *    may have launched part of their kernels when they return an error.
+ *  - Stream order is kept: results of a call are visible to whatever follows it on the same
+ *    stream.  Kernels are launched with programmatic stream serialisation (their set-up may
+ *    overlap the tail of the kernel before them on the stream; they wait for that kernel to
+ *    complete before they touch global memory), which a caller's own kernels, copies and
+ *    events on the stream need not know about.  Calls may be captured into a CUDA graph.
  *  - Citations "K/x.py" are packages/lczero-triton/src/lczero_triton/bt4/kernels/x.py,
  *    "N" is packages/lczero-triton/src/lczero_triton/bt4/network.py and "T/x.py" is
  *    packages/lczero-triton/tests/x.py of the reference.
