@@ -21,7 +21,7 @@
  *    stream.  Kernels are launched with programmatic stream serialisation (their set-up may
  *    overlap the tail of the kernel before them on the stream; they wait for that kernel to
  *    complete before they touch global memory), which a caller's own kernels, copies and
- *    events on the stream need not know about.  Calls may be captured into a CUDA graph.
+ *    events on the stream need not know about.
  *  - Citations "K/x.py" are packages/lczero-triton/src/lczero_triton/bt4/kernels/x.py,
  *    "N" is packages/lczero-triton/src/lczero_triton/bt4/network.py and "T/x.py" is
  *    packages/lczero-triton/tests/x.py of the reference.
