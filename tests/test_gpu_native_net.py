@@ -125,3 +125,38 @@ def test_object_rejects_misuse(pkg) -> None:
     bad = pkg["native"].NetConfigC.from_config(cfg)
     bad.heads = 3
     assert lib.lc0b200_net_arena_bytes(ctypes.byref(bad), 4) == 0
+
+
+@pytest.mark.parametrize("mode", ["bf16", "int8"])
+@pytest.mark.parametrize(("cfg_name", "batch"), [("TINY", 32), ("BT4", 64), ("BT4", 192)])
+def test_replayed_graph_and_back_to_back_launches_equal_one_forward(pkg, cfg_name, batch, mode) -> None:
+    """The forward as the benchmark runs it: captured once into a CUDA graph and replayed.  Every kernel may be
+    scheduled while its predecessor on the stream is still running (programmatic dependent launch) and waits
+    for it before touching memory; a kernel that touched memory too early would show here as results that depend
+    on timing: five launches in a row, a graph replay, and a replay on new planes written into the same input
+    buffers must each equal one forward on its own, bit for bit."""
+    cfg = getattr(pkg["config"], cfg_name)
+    weights = pkg["weights"].random_weights(cfg, 5)
+    net = pkg["native"].NativeNet(weights, cfg, max_batch=batch, mode=mode)
+    masks, values = (x.cuda() for x in pkg["synthetic"].synthetic_planes(batch, 5))
+    other_masks, other_values = (x.cuda() for x in pkg["synthetic"].synthetic_planes(batch, 6))
+    alone = [x.clone() for x in net.forward(masks, values)]
+    torch.cuda.synchronize()
+    other_alone = [x.clone() for x in net.forward(other_masks, other_values)]
+    torch.cuda.synchronize()
+    assert not torch.equal(alone[0], other_alone[0])
+    for _ in range(5):
+        again = net.forward(masks, values)
+    assert all(torch.equal(a, b) for a, b in zip(alone, again))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = net.forward(masks, values)
+    for _ in range(3):
+        graph.replay()
+    assert all(torch.equal(a, b) for a, b in zip(alone, captured))
+    masks.copy_(other_masks)
+    values.copy_(other_values)
+    graph.replay()
+    assert all(torch.equal(a, b) for a, b in zip(other_alone, captured))
+    _no_timeouts(pkg)
+    net.close()
