@@ -3,6 +3,7 @@
 Run on a machine with a GPU and the unmodified reference package installed under ``baseline/_ref``:
 
     python tests/golden/make_network_golden.py [output.npz]        # needs a GPU
+    python tests/golden/make_network_golden.py [output.npz] --only bt4_b64   # one case, merged into the file
     python tests/golden/make_network_golden.py --dry               # no GPU: walks the graph, launches nothing,
                                                                    # writes reference_program_plan.json
 
@@ -51,7 +52,7 @@ ROOT = pathlib.Path(__file__).resolve().parents[2]
 sys.path[:0] = [str(ROOT / "baseline" / "_ref"), str(ROOT)]
 
 # (config name, batch, seed).  Batches are small: the reference autotunes every kernel specialisation.
-CASES = (("tiny", 5, 11), ("tiny", 64, 12), ("bt3", 3, 13), ("bt4", 2, 14))
+CASES = (("tiny", 5, 11), ("tiny", 64, 12), ("bt3", 3, 13), ("bt4", 2, 14), ("bt4", 64, 15))
 
 TOP_LEVEL = {
     "weights.ip_emb_preproc_w": "/attn_body/embedding/preprocess/matmul/w",
@@ -388,7 +389,8 @@ def run_program(builder, program, persistent: dict[str, torch.Tensor], inputs: d
 
 def main(argv: list[str]) -> None:
     dry = "--dry" in argv
-    positional = [a for a in argv if not a.startswith("--")]
+    only = argv[argv.index("--only") + 1] if "--only" in argv else None
+    positional = [a for i, a in enumerate(argv) if not a.startswith("--") and (i == 0 or argv[i - 1] != "--only")]
     target = pathlib.Path(positional[0]) if positional else pathlib.Path(__file__).with_name("reference_network_outputs.npz")
     stub_generated_protobuf_modules()
     from lczero_triton_b200 import config as C
@@ -396,8 +398,13 @@ def main(argv: list[str]) -> None:
     from lczero_triton_b200 import weights as W
 
     out: dict[str, np.ndarray] = {}
+    if only is not None and not dry and target.exists():
+        with np.load(target) as existing:
+            out.update({key: existing[key] for key in existing.files})
     plans: dict[str, dict] = {}
     for cfg_name, batch, seed in CASES:
+        if only is not None and f"{cfg_name}_b{batch}" != only:
+            continue
         cfg = C.CONFIGS[cfg_name]
         started = time.time()
         builder, program, consumed = build_program(cfg, batch, dry=dry)
@@ -432,7 +439,7 @@ def main(argv: list[str]) -> None:
         np.savez_compressed(target, **out)  # after every case: a later case that fails keeps the earlier ones
     if dry:
         plan_target = pathlib.Path(__file__).with_name("reference_program_plan.json")
-        keep = {key: plans[key] for key in ("tiny_b5", "bt4_b2")}
+        keep = {key: plans[key] for key in ("tiny_b5", "bt4_b2") if key in plans}
         plan_target.write_text(json.dumps(keep, separators=(",", ":")))
         print(f"wrote {plan_target} ({plan_target.stat().st_size} bytes)")
     else:
