@@ -75,14 +75,21 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def halt(self) -> None:
+        """Stop sampling (the summary is made by stop())."""
+        if self.proc is not None and self.proc.poll() is None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        self.halt()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         sm, sm_max, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.lines:
@@ -130,8 +137,12 @@ def _max_over_ranks(value: float, dist) -> float:
     return float(t.item())
 
 
-def _timed_steps(step, warmup: int, steps: int, dist) -> float:
-    """Milliseconds for exactly `steps` calls of `step`, CUDA events on the current stream, max over ranks."""
+def _timed_steps(step, warmup: int, steps: int, dist, sampler: "ClockSampler | None" = None) -> float:
+    """Milliseconds for exactly `steps` calls of `step`, CUDA events on the current stream, max over ranks.
+    A clock sampler, if given, runs from the first warm-up step to the end of the timed steps: every sample is
+    taken with the GPU under this load (set-up, graph capture and the barriers' waits are outside)."""
+    if sampler is not None:
+        sampler.start()
     for _ in range(warmup):
         step()
     _barrier(dist)
@@ -141,6 +152,8 @@ def _timed_steps(step, warmup: int, steps: int, dist) -> float:
         step()
     stop.record()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.halt()
     _barrier(dist)
     return _max_over_ranks(start.elapsed_time(stop), dist)
 
@@ -211,14 +224,15 @@ def _graph_step(fn):
         return fn, repr(exc)[:160]
 
 
-def _forward_rate(net, masks_d, values_d, batch: int, world: int, args, dist, *, graph: bool = True) -> dict:
+def _forward_rate(net, masks_d, values_d, batch: int, world: int, args, dist, *, graph: bool = True,
+                  sampler: "ClockSampler | None" = None) -> dict:
     """Device-resident positions/s of `net` on one batch: whole-job value, max over ranks."""
     def eager() -> None:
         net.forward(masks_d, values_d)
 
     eager()
     step, error = _graph_step(eager) if graph else (eager, None)
-    total_ms = _timed_steps(step, args.warmup, args.steps, dist)
+    total_ms = _timed_steps(step, args.warmup, args.steps, dist, sampler)
     out = {"value": world * batch * args.steps / (total_ms * 1e-3), "unit": "positions/s",
            "ms_per_step": total_ms / args.steps, "batch_per_gpu": batch,
            "launch": "CUDA graph replay" if graph and error is None else "eager launches"}
@@ -423,8 +437,7 @@ def run(args) -> None:
     net.forward(masks_d, values_d)
     launches_per_step = _lib.launch_count() - launches_before
     sampler = ClockSampler(local)
-    sampler.start()
-    head = _forward_rate(net, masks_d, values_d, batch, world, args, dist, graph=bool(args.graph))
+    head = _forward_rate(net, masks_d, values_d, batch, world, args, dist, graph=bool(args.graph), sampler=sampler)
     clocks = sampler.stop()
     e2e = _e2e_rate(net, masks_h, values_h, batch, world, args, dist)
 

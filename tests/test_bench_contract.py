@@ -37,7 +37,8 @@ def test_other_ranks_of_the_reference_arm_stay_silent(monkeypatch, capsys) -> No
 
 def test_clock_sampler_summarises_nvidia_smi_lines() -> None:
     sampler = bench.ClockSampler(0)
-    sampler.proc = type("P", (), {"terminate": lambda self: None, "wait": lambda self, timeout=None: 0})()
+    sampler.proc = type("P", (), {"terminate": lambda self: None, "wait": lambda self, timeout=None: 0,
+                                  "poll": lambda self: None})()
     sampler.lines = [
         "0, 1335, 1965, 990.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
         "0, 1290, 1965, 998.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
@@ -47,3 +48,24 @@ def test_clock_sampler_summarises_nvidia_smi_lines() -> None:
     summary = sampler.stop()
     assert summary["sm_mhz"] == 1335.0 and summary["sm_max_mhz"] == 1965.0 and summary["samples"] == 3
     assert summary["reasons"] == ["sw_power_cap"]
+
+
+def test_clock_sampler_runs_only_around_warm_up_and_timed_steps(monkeypatch) -> None:
+    """The sampler is started by the timing loop itself and halted before the closing barrier, so that what it
+    reports is the clock under the measured load, not the idle clock during set-up or while other ranks finish."""
+    events: list[str] = []
+    sampler = bench.ClockSampler(0)
+    monkeypatch.setattr(sampler, "start", lambda: events.append("start"))
+    monkeypatch.setattr(sampler, "halt", lambda: events.append("halt"))
+    monkeypatch.setattr(bench, "_barrier", lambda dist: events.append("barrier"))
+    monkeypatch.setattr(bench, "_max_over_ranks", lambda value, dist: value)
+
+    class _Event:
+        def __init__(self, enable_timing=True): pass
+        def record(self): events.append("record")
+        def elapsed_time(self, other): return 1.0
+
+    monkeypatch.setattr(bench.torch.cuda, "Event", _Event)
+    monkeypatch.setattr(bench.torch.cuda, "synchronize", lambda: events.append("sync"))
+    bench._timed_steps(lambda: events.append("step"), 3, 2, None, sampler)
+    assert events == ["start", "step", "step", "step", "barrier", "record", "step", "step", "record", "sync", "halt", "barrier"]
