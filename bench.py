@@ -3,6 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|int8] [--batch B]
     python bench.py --impl reference ...      # the CPU fp32 forward on the host cores
+    python bench.py --impl reference-gpu      # the reference's own 291-node program on the GPU (batch <= 2047)
 
 One "step" is one forward pass over one batch of synthetic positions (seeded planes,
 N(0, 0.02) random-init weights of the BT4 shape; the trained network and lc0's benchmark
@@ -209,6 +210,64 @@ def run_reference(args) -> None:
         "e2e": {"value": rate, "unit": "positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(args) -> None:
+    """An extra arm, not part of the two-arm contract: the UNMODIFIED reference package under ``baseline/_ref``
+    building its own program (its graph builder, Triton kernels, compile functions, allocation plan) and that
+    program replayed on this GPU by the small runtime of ``tests/golden/make_network_golden.py``.  The
+    reference's batched kernels cannot be launched above 2047 positions, so the workload is the BT4 shape at
+    min(batch, 2047) positions; building the program autotunes its kernels (about four minutes)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import importlib.util
+
+    def unavailable(why: str) -> None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": why}), flush=True)
+
+    if not (ROOT / "baseline" / "_ref" / "lczero_triton").exists():
+        return unavailable("baseline/_ref holds no reference install")
+    try:
+        import triton  # noqa: F401
+    except ImportError:
+        return unavailable("triton is not importable")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    spec = importlib.util.spec_from_file_location("make_network_golden", ROOT / "tests" / "golden" / "make_network_golden.py")
+    runtime = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(runtime)
+    runtime.stub_generated_protobuf_modules()
+    from lczero_triton_b200.config import BT4
+    from lczero_triton_b200.synthetic import synthetic_planes
+    from lczero_triton_b200.weights import random_weights
+
+    torch.cuda.set_device(0)
+    batch = min(args.batch, 65535 // BT4.heads)
+    weights = runtime.exact_in_both(random_weights(BT4, 0))
+    masks, values = (x.cuda() for x in synthetic_planes(batch, 1000))
+    started = time.time()
+    builder, program, _ = runtime.build_program(BT4, batch, dry=False)
+    built = time.time() - started
+    loaded = runtime.LoadedProgram(builder, program, {n: w.float().half().cuda() for n, w in weights.items()},
+                                   {"/input/plane_masks": masks, "/input/plane_values": values}, fill=0)
+    loaded.launch()
+    step, _ = _graph_step(loaded.launch)
+    sampler = ClockSampler(0)
+    ms = _timed_steps(step, args.warmup, args.steps, None, sampler)
+    clocks = sampler.stop()
+    rate = batch * args.steps / (ms * 1e-3)
+    line = {
+        "impl": "reference-gpu", "metric": METRIC, "value": rate, "unit": "positions/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"BT4-shape forward (E1024 L15 H32 F1536 smolgen 32->256), batch {batch}: the reference's "
+                               f"program of {loaded.info['nodes']} kernel launches, replayed from a CUDA graph",
+                   "batch_per_gpu": batch, "graph_build_s": round(built, 1),
+                   "l2": "working set per step (GBs of activations) far exceeds the 126 MB L2"},
+        "clocks": clocks, "gpu_launches": 0, "reference_launches": loaded.info["nodes"] * args.steps,
+    }
+    loaded.close()
     print(json.dumps(line), flush=True)
 
 
@@ -752,7 +811,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
     ap.add_argument("--mode", default="bf16", choices=["bf16", "int8"])
     ap.add_argument("--batch", type=int, default=4096, help="positions per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -781,6 +840,8 @@ def main() -> None:
         return
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     elif args.gpus > 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_one_process(args)
     else:

@@ -69,3 +69,13 @@ def test_clock_sampler_runs_only_around_warm_up_and_timed_steps(monkeypatch) -> 
     monkeypatch.setattr(bench.torch.cuda, "synchronize", lambda: events.append("sync"))
     bench._timed_steps(lambda: events.append("step"), 3, 2, None, sampler)
     assert events == ["start", "step", "step", "step", "barrier", "record", "step", "step", "record", "sync", "halt", "barrier"]
+
+
+def test_reference_gpu_arm_says_unavailable_without_a_device(monkeypatch, capsys) -> None:
+    """The extra arm (the reference's own program on the GPU) never falls back to anything: without a CUDA
+    device, Triton or the reference install it prints one line saying which is missing."""
+    monkeypatch.delenv("RANK", raising=False)
+    monkeypatch.setattr(bench.torch.cuda, "is_available", lambda: False)
+    bench.run_reference_gpu(type("A", (), {"batch": 4096, "steps": 2, "warmup": 1})())
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["impl"] == "reference-gpu" and "unavailable" in line
