@@ -1008,9 +1008,11 @@ int launch(const lc0b200_gemm_args& g, cudaStream_t stream) {
   return LC0B200_OK;
 }
 
-// Rows at and above which the 256-wide tiles are shared by CTA pairs (below it there are too few
-// 256 x 256 tiles to fill 74 pairs and the single-CTA kernel balances better).
-constexpr long long kPairMinRows = 8192;
+// Rows at and above which the 256-wide tiles are shared by CTA pairs.  bf16: whenever the tile width is 256
+// at all (measured from 24 positions up: 2 % faster at batch 32, 4 % at 64, 6 % at 120, level below); int8:
+// from 8192 rows (below that the two forms measure the same within half a percent).
+constexpr long long kPairMinRowsBf16 = 256;
+constexpr long long kPairMinRowsInt8 = 8192;
 
 template <bool INT8, bool W_KN, int MODE>
 int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
@@ -1026,7 +1028,7 @@ int dispatch_bn(const lc0b200_gemm_args& g, cudaStream_t stream) {
   while (bn > kMinBn && (bn / 2 >= g.n || tiles(bn) < enough)) bn /= 2;
   if (bn == 256) {
     // (Short main loops are paced by the output and measured faster on single CTAs.)
-    if (g.m >= kPairMinRows && g.k > 512) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
+    if (g.m >= (INT8 ? kPairMinRowsInt8 : kPairMinRowsBf16) && g.k > 512) return launch<256, INT8, W_KN, 2, MODE>(g, stream);
     return launch<256, INT8, W_KN, 1, MODE>(g, stream);
   }
   if constexpr (kMinBn <= 128) {

@@ -55,7 +55,8 @@ SHAPES = [
     (128, 256, 64), (128, 256, 1024), (256, 1024, 1024), (1024, 1536, 1024), (640, 1024, 1536),
     (512, 3072, 1024), (300, 1000, 520), (64, 32768, 768), (4096, 32, 1024), (4096, 16, 128),
     (77, 64, 2048), (130, 128, 8192), (2048, 4096, 256), (33, 8192, 256), (1000, 1024, 624), (5, 128, 128),
-    # 8192 rows and more with a wide output: 256 x 256 tiles shared by CTA pairs
+    # many rows with a wide output: 256 x 256 tiles shared by CTA pairs (bf16: whenever the tile is 256 wide and
+    # K > 512, so several of the smaller shapes above run on pairs too; int8: from 8192 rows)
     (8200, 1536, 1024), (16384, 3072, 1024), (8192, 1000, 520), (9000, 4096, 256),
     # a ragged last tile narrower than the tile: its MMAs cover 32 / 96 / 160 columns instead of 256
     (300, 800, 256), (8200, 1056, 1024), (8200, 1120, 1024), (700, 3232, 1024), (8192, 3104, 1024),
