@@ -58,6 +58,7 @@ SHAPES = [
     # many rows with a wide output: 256 x 256 tiles shared by CTA pairs (bf16: whenever the tile is 256 wide and
     # K > 512, so several of the smaller shapes above run on pairs too; int8: from 8192 rows)
     (8200, 1536, 1024), (16384, 3072, 1024), (8192, 1000, 520), (9000, 4096, 256),
+    (900, 3104, 1024), (1300, 2048, 1024), (3000, 1024, 1024),  # few rows on pairs, the last pair half empty
     # a ragged last tile narrower than the tile: its MMAs cover 32 / 96 / 160 columns instead of 256
     (300, 800, 256), (8200, 1056, 1024), (8200, 1120, 1024), (700, 3232, 1024), (8192, 3104, 1024),
 ]

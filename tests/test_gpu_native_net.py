@@ -84,6 +84,41 @@ def test_bt4_shape_through_the_c_object_matches_the_python_network(pkg) -> None:
     native.close()
 
 
+@pytest.mark.parametrize("batch", [15, 30, 77])
+def test_bt4_row_counts_that_leave_a_cta_pair_half_empty(pkg, batch) -> None:
+    """960, 1920 and 4928 token rows: the 256-wide GEMM tiles run as 256-row tiles of two CTAs, and the last tile
+    of each GEMM is ragged (only part of the first CTA's rows, or of the second's, exist).  Every position
+    against the fp32 oracle, against the last positions run alone, and bit for bit against the same positions as the
+    tail of a larger batch."""
+    cfg = pkg["config"].BT4
+    weights = pkg["weights"].random_weights(cfg, 4)
+    masks, values = pkg["synthetic"].synthetic_planes(batch, 4)
+    native = pkg["native"].NativeNet(weights, cfg, max_batch=batch)
+    got = [x.cpu() for x in native.forward(masks.cuda(), values.cuda())]
+    _no_timeouts(pkg)
+    native.close()
+    want = O.forward(weights, cfg, masks, values, table=pkg["table"])
+    rounded = O.forward(weights, cfg, masks, values, table=pkg["table"], round_to=torch.bfloat16)
+    for a, w, r in zip(got, want, rounded):
+        err, floor = float((a - w).abs().max()), float((r - w).abs().max())
+        assert err <= 1.5e-2 and err <= 2.0 * floor + 2e-3, (err, floor)
+    # Positions are independent: the last three alone give the same numbers up to bf16 rounding flips (a batch of
+    # three runs narrow GEMM tiles, whose epilogue combines its per-column vectors in another order than the wide
+    # tiles'; from 15 positions up every batch size gives the same bits, which the next lines hold for 16 more).
+    alone = pkg["native"].NativeNet(weights, cfg, max_batch=3)
+    tail = [x.cpu() for x in alone.forward(masks[-3:].cuda(), values[-3:].cuda())]
+    alone.close()
+    for a, b, w in zip(got, tail, want):
+        assert float((a[-3:] - b).abs().max()) < 0.15 * float(w.std().clamp_min(1e-6)) + 2e-3
+    wider = pkg["native"].NativeNet(weights, cfg, max_batch=batch + 16)
+    more_masks, more_values = pkg["synthetic"].synthetic_planes(batch + 16, 9)
+    more_masks[-batch:], more_values[-batch:] = masks, values
+    again = [x.cpu() for x in wider.forward(more_masks.cuda(), more_values.cuda())]
+    wider.close()
+    for a, b in zip(got, again):
+        assert torch.equal(a, b[-batch:])
+
+
 @pytest.mark.parametrize("name", ["TINY", "BT4"])
 def test_int8_mode_through_the_c_object_equals_the_python_network(pkg, name) -> None:
     """int8 GEMMs, stand-alone LayerNorms: nothing is summed differently on the two sides (the weights
